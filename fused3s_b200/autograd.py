@@ -68,18 +68,20 @@ def attention(q, k, v, plan: TrainingPlan, scale_divisor: float = 1.0):
 class _ShardedFusedAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q_local, k_local, v_local, att, scale_divisor: float):
-        out = att.forward(q_local, k_local, v_local, scale_divisor)
+        out, ctx.saved = att.forward_save(q_local, k_local, v_local, scale_divisor)
         ctx.att = att
         return out
 
     @staticmethod
     def backward(ctx, d_out):
-        dq, dk, dv = ctx.att.backward(d_out, grad_dtype=torch.float16)
+        dq, dk, dv = ctx.att.backward_from(ctx.saved, d_out, grad_dtype=torch.float16)
+        ctx.saved = None
         return dq, dk, dv, None, None
 
 
 def sharded_attention(q_local, k_local, v_local, att, scale_divisor: float = 1.0):
     """Differentiable attention over a graph whose rows are divided over the ranks: ``att`` is this
     rank's ``fused3s_b200.sharding.ShardedTrainingAttention``; inputs and gradients are the rank's own
-    rows (fp16), the collectives run inside.  One forward may be outstanding per ``att`` at a time."""
+    rows (fp16), the collectives run inside.  Every call keeps its own saved tensors, so one ``att`` may be
+    shared by several layers or micro-batches."""
     return _ShardedFusedAttention.apply(q_local, k_local, v_local, att, scale_divisor)

@@ -23,6 +23,7 @@ ERR_DEVICE = -5
 EXPORTS = (
     "f3s_version",
     "f3s_last_error_string",
+    "f3s_kernel_launch_count",
     "f3s_preprocess_workspace_bytes",
     "f3s_preprocess_count",
     "f3s_preprocess_count_rect",
@@ -33,6 +34,11 @@ EXPORTS = (
     "f3s_forward_static",
     "f3s_forward_traced",
     "f3s_forward_lse",
+    "f3s_forward_status",
+    "f3s_forward_static_status",
+    "f3s_status_word_to_code",
+    "f3s_debug_set_unit_list_limit",
+    "f3s_validate_plan",
     "f3s_backward_workspace_bytes",
     "f3s_backward",
     "f3s_backward_prepare",
@@ -40,6 +46,7 @@ EXPORTS = (
     "f3s_backward_dq",
     "f3s_backward_dkv",
     "f3s_partition_row_windows",
+    "f3s_probe_gather_rows",
 )
 
 
@@ -62,6 +69,7 @@ def lib() -> C.CDLL:
         vp, i32, i64, sz, f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_size_t, C.c_float
         l.f3s_version.restype = C.c_int
         l.f3s_last_error_string.restype = C.c_char_p
+        l.f3s_kernel_launch_count.restype = C.c_uint64
         l.f3s_preprocess_workspace_bytes.restype = sz
         l.f3s_preprocess_workspace_bytes.argtypes = [i64, i64, C.c_int]
         l.f3s_preprocess_count.restype = C.c_int
@@ -90,6 +98,16 @@ def lib() -> C.CDLL:
         l.f3s_forward_lse.restype = C.c_int
         l.f3s_forward_lse.argtypes = [vp, vp, vp, vp, i32, i32, i64, i32, i32, i32, i64, vp, vp, vp, f32, vp, vp, vp,
                                       sz, vp]
+        l.f3s_forward_status.restype = C.c_int
+        l.f3s_forward_status.argtypes = [vp, vp, vp]
+        l.f3s_forward_static_status.restype = C.c_int
+        l.f3s_forward_static_status.argtypes = [vp, vp]
+        l.f3s_status_word_to_code.restype = C.c_int
+        l.f3s_status_word_to_code.argtypes = [i32]
+        l.f3s_debug_set_unit_list_limit.restype = None
+        l.f3s_debug_set_unit_list_limit.argtypes = [i32]
+        l.f3s_validate_plan.restype = C.c_int
+        l.f3s_validate_plan.argtypes = [vp, vp, vp, i32, i64, i32, i32, vp, sz, vp]
         l.f3s_backward_workspace_bytes.restype = sz
         l.f3s_backward_workspace_bytes.argtypes = [i32, i64, i64, i32, i32, i32]
         l.f3s_backward.restype = C.c_int
@@ -105,6 +123,8 @@ def lib() -> C.CDLL:
         l.f3s_backward_dkv.restype = C.c_int
         l.f3s_backward_dkv.argtypes = [vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, i64, vp, vp, i64, vp, vp, vp, f32,
                                        vp, vp, i32, vp, sz, vp]
+        l.f3s_probe_gather_rows.restype = C.c_int
+        l.f3s_probe_gather_rows.argtypes = [vp, i64, vp, i64, vp, vp]
         l.f3s_partition_row_windows.restype = C.c_int
         l.f3s_partition_row_windows.argtypes = [vp, i32, i32, vp]
         _lib = l
@@ -232,6 +252,30 @@ class ForwardPlan:
                                  self.heads, self.dim, self.ld, _ptr(self.q), _ptr(self.k),
                                  _ptr(self.v), self.scale_divisor, self.apply_softmax, _ptr(self.out),
                                  _ptr(self.sddmm), _ptr(self.ws), self.ws_bytes, s))
+
+
+    def status(self, stream=None) -> None:
+        """Blocks until the plan's stream has drained and raises ``F3SError`` (``ERR_DEVICE``) if a
+        kernel of the last launch reported that it could not finish (``f3s_forward_status``)."""
+        s = _stream(self.dev) if stream is None else C.c_void_p(stream)
+        check(self.l.f3s_forward_status(_ptr(self.ws), None, s))
+
+
+def validate_plan(tcb: dict, num_kv_rows: int, scheduled: bool = True) -> None:
+    """``f3s_validate_plan``: raises ``F3SError`` (``ERR_INVALID_ARG``) if the plan holds an index the
+    kernels would dereference out of range for K / V tensors of ``num_kv_rows`` rows.  For plans that
+    were read from a file or assembled from parts; blocks until the answer is known."""
+    import torch
+
+    bw = tcb["block_w"]
+    rwo = tcb["rowWindowOffset"]
+    dev = rwo.device
+    with torch.cuda.device(dev):
+        scratch = torch.empty(16, dtype=torch.uint8, device=dev)
+        check(lib().f3s_validate_plan(_ptr(rwo), _ptr(tcb["sortedRowWindows"] if scheduled else None),
+                                      _ptr(tcb["sparseAToXidx"]), rwo.numel() - 1,
+                                      tcb["sparseAToXidx"].numel() // bw, bw, int(num_kv_rows), _ptr(scratch), 16,
+                                      _stream(dev)))
 
 
 def forward(tcb: dict, num_nodes: int, q, k, v, scale_divisor: float = 1.0, apply_softmax: bool = True,
@@ -423,16 +467,55 @@ def forward_static(tcb: dict, num_nodes: int, q, k, v, out, scale_divisor: float
                    scheduled: bool = True) -> None:
     """``f3s_forward_static``: the fused forward for callers that may not allocate device memory.
     Its scratch is a fixed array inside the library, so nothing is allocated here either: the caller
-    passes every buffer, including ``out`` (fp32, shape of ``q``).  Calls on one device must not
-    overlap on the GPU."""
-    heads = q.shape[1] if q.dim() == 3 else 1
-    dim = q.shape[-1]
+    passes every buffer, including ``out`` (fp32, contiguous, shape ``(num_nodes,) + q.shape[1:]``, on the
+    device of ``q``).  Q, K and V may be strided row views (one shared row stride), as everywhere else.
+    Calls on one device must not overlap on the GPU."""
+    import torch
+
+    heads, dim, ld = _row_stride(q, k, v)
     bw = tcb["block_w"]
-    check(lib().f3s_forward_static(
-        _ptr(tcb["rowWindowOffset"]), _ptr(tcb["sortedRowWindows"] if scheduled else None), _ptr(tcb["sparseAToXidx"]),
-        _ptr(tcb["tcbBitMap"]), num_nodes, tcb["rowWindowOffset"].numel() - 1, tcb["sparseAToXidx"].numel() // bw, bw,
-        heads, dim, heads * dim, _ptr(q), _ptr(k), _ptr(v), float(scale_divisor), 1 if apply_softmax else 0,
-        _ptr(out), _stream(q.device)))
+    want_shape = (num_nodes,) + tuple(q.shape[1:])
+    if out.dtype != torch.float32 or not out.is_contiguous() or tuple(out.shape) != want_shape or out.device != q.device:
+        raise F3SError(ERR_INVALID_ARG, f"out must be a contiguous fp32 tensor of shape {want_shape} on {q.device}")
+    with torch.cuda.device(q.device):  # the built-in scratch is looked up on the current device
+        check(lib().f3s_forward_static(
+            _ptr(tcb["rowWindowOffset"]), _ptr(tcb["sortedRowWindows"] if scheduled else None),
+            _ptr(tcb["sparseAToXidx"]), _ptr(tcb["tcbBitMap"]), num_nodes, tcb["rowWindowOffset"].numel() - 1,
+            tcb["sparseAToXidx"].numel() // bw, bw, heads, dim, ld, _ptr(q), _ptr(k), _ptr(v), float(scale_divisor),
+            1 if apply_softmax else 0, _ptr(out), _stream(q.device)))
+
+
+def forward_static_status(device) -> None:
+    """``f3s_forward_static_status``: blocks, then raises if the last ``forward_static`` call on
+    ``device`` reported a device-side failure."""
+    import torch
+
+    with torch.cuda.device(device):
+        check(lib().f3s_forward_static_status(None, _stream(torch.device(device))))
+
+
+def gather_rate_gbs(table_bytes: int, device, n_ids: int = 1 << 24, repeats: int = 5) -> float:
+    """GB/s at which ``f3s_probe_gather_rows`` gathers 128-byte rows at seeded random ids from a table
+    of ``table_bytes`` bytes on ``device`` (best of ``repeats``, CUDA events): the L2 ceiling for the
+    fused kernel's gathers when the table fits the cache, the HBM gather ceiling when it does not."""
+    import torch
+
+    dev = torch.device(device)
+    rows = max(1, int(table_bytes) // 128)
+    with torch.cuda.device(dev):
+        gen = torch.Generator(device=dev).manual_seed(7)
+        table = torch.zeros(rows * 32, dtype=torch.int32, device=dev)
+        ids = torch.randint(0, rows, (n_ids,), dtype=torch.int32, device=dev, generator=gen)
+        sink = torch.zeros(1, dtype=torch.int32, device=dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        best = float("inf")
+        for _ in range(repeats + 1):  # the first call warms the table into the cache
+            e0.record()
+            check(lib().f3s_probe_gather_rows(_ptr(table), rows, _ptr(ids), n_ids, _ptr(sink), _stream(dev)))
+            e1.record()
+            e1.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+    return 128.0 * (n_ids // 32 * 32) / (best * 1e-3) / 1e9
 
 
 def partition_row_windows(rwo_host, n_parts: int):

@@ -126,7 +126,15 @@ plan_kernel(const int *__restrict__ rwo, const int *__restrict__ sorted, int n_r
         units[unit0 + c] = d;
       }
     } else {
+      // Does not fit: report it, and leave no unwritten entry below the capacity (consumers skip
+      // entries whose window is negative).  The window's rows stay unwritten; the host learns why.
       atomicExch(&hdr[HDR_STATUS], STATUS_LIST_OVERFLOW);
+      UnitDesc d;
+      d.window = -1;
+      d.t8_begin = d.t8_end = d.slot_base = d.chunk = 0;
+      d.n_chunks = 1;
+      d.pad0 = d.pad1 = 0;
+      for (int c = 0; c < nch && unit0 + c < max_units; ++c) units[unit0 + c] = d;
     }
   }
   int inv = (i < n_rw && !heavy) ? n_rw - i : 0;
@@ -174,7 +182,7 @@ struct UnitSource {
       u_heavy = 0;
       first_light = 0;
     } else {
-      u_heavy = p.hdr[HDR_U_HEAVY];
+      u_heavy = min(p.hdr[HDR_U_HEAVY], p.max_slots);  // a list that overflowed holds max_slots entries at most
       first_light = p.n_rw - p.hdr[HDR_LIGHT_INV];
     }
     n_units = u_heavy + (p.n_rw - first_light);
@@ -203,6 +211,7 @@ struct UnitSource {
       u.n_chunks = 1;
       if (uu < u_heavy) {
         const UnitDesc d = p.units[uu];
+        if (d.window < 0) continue;  // placeholder of a window the list had no room for
         u.window = d.window; u.t8b = d.t8_begin; u.t8e = d.t8_end;
         u.slot_base = d.slot_base; u.chunk = d.chunk; u.n_chunks = d.n_chunks;
         return true;
@@ -238,7 +247,7 @@ struct BatchedUnitSource {
       u_heavy = 0;
       first_light = 0;
     } else {
-      u_heavy = p.hdr[HDR_U_HEAVY];
+      u_heavy = min(p.hdr[HDR_U_HEAVY], p.max_slots);  // a list that overflowed holds max_slots entries at most
       first_light = p.n_rw - p.hdr[HDR_LIGHT_INV];
     }
     n_units = u_heavy + (p.n_rw - first_light);

@@ -417,7 +417,7 @@ static int launch_bwd(const BwdParams &p, int grid, cudaStream_t stream) {
   auto kern = bwd_kernel<D, NT8, STAGES, WARPS, DKV, FSPLIT>;
   F3S_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
   kern<<<grid, WARPS * 32, C::SMEM_BYTES, stream>>>(p);
-  F3S_CUDA_TRY(cudaGetLastError());
+  F3S_CHECK_LAUNCH();
   return F3S_OK;
 }
 
@@ -445,7 +445,7 @@ static int run_bwd(BwdParams p, const BwdSched &sc, unsigned char *ws, const Bwd
       plan_kernel<<<(p.n_rw + PLAN_THREADS - 1) / PLAN_THREADS, PLAN_THREADS, 0, stream>>>(
           p.rwo, p.sorted, p.n_rw, p.t8_per_tcb, sc.ch8, kc.nt8, p.hdr, reinterpret_cast<UnitDesc *>(ws + sc.off_units),
           sc.max_slots);
-      F3S_CUDA_TRY(cudaGetLastError());
+      F3S_CHECK_LAUNCH();
     }
     int rc = F3S_ERR_UNSUPPORTED;
     if (kc.d_pad == 32) rc = dkv ? launch_bwd<32, 4, 3, 8, true, 1>(p, grid, stream) : launch_bwd<32, 4, 3, 8, false, 1>(p, grid, stream);
@@ -513,7 +513,7 @@ extern "C" int f3s_backward(const int32_t *row_window_offset, const int32_t *sor
   float2 *stats = reinterpret_cast<float2 *>(ws + L.off_stats);
   const long long pairs = (long long)num_nodes * heads;
   bwd_prepare_kernel<<<(unsigned)((pairs + 7) / 8), 256, 0, stream>>>(out, d_out, lse, do_h, stats, pairs, head_dim);
-  F3S_CUDA_TRY(cudaGetLastError());
+  F3S_CHECK_LAUNCH();
 
   BwdParams p;
   p.n_nodes = num_nodes;
@@ -586,7 +586,7 @@ extern "C" int f3s_backward_prepare(const float *out, const float *d_out, const 
   const long long pairs = (long long)num_rows * heads;
   bwd_prepare_kernel<<<(unsigned)((pairs + 7) / 8), 256, 0, stream>>>(out, d_out, lse, static_cast<__half *>(d_out_f16),
                                                                       reinterpret_cast<float2 *>(stats), pairs, head_dim);
-  F3S_CUDA_TRY(cudaGetLastError());
+  F3S_CHECK_LAUNCH();
   return F3S_OK;
 }
 

@@ -33,6 +33,14 @@ int sm_count();
     }                                  \
   } while (0)
 
+// After every kernel launch: counts it (f3s_kernel_launch_count) and turns a launch error into a status.
+void note_launches(int n);
+#define F3S_CHECK_LAUNCH()                  \
+  do {                                      \
+    ::f3s::note_launches(1);                \
+    F3S_CUDA_TRY(cudaGetLastError());       \
+  } while (0)
+
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 #ifdef __CUDACC__

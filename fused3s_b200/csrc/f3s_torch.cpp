@@ -175,6 +175,8 @@ std::vector<torch::Tensor> run_forward(const torch::Tensor &rwo, const c10::opti
     cudaEventDestroy(e1);
   }
   check_status(rc, "f3s_forward");
+  // the timed ops have synchronised already, so asking the kernels how they fared costs one small copy
+  if (opt.timed) check_status(f3s_forward_status(ws.data_ptr(), nullptr, stream.stream()), "f3s_forward (device status)");
   if (opt.sm_time_file != nullptr) write_sm_times(trace.cpu(), opt.sm_time_file);
   auto time = torch::tensor(ms, torch::TensorOptions().dtype(torch::kFloat32));
   return {time, out, sddmm};

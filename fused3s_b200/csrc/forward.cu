@@ -462,6 +462,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) fwd_kernel_coop(const FwdParams
   ws.init(smem_raw + warp * C::WARP_BYTES, lane);
   float *my_part = reinterpret_cast<float *>(smem_raw + warp * C::WARP_BYTES);
 
+  // One-launch mode has no memset and no schedule kernel: nothing here can fail, so the status word
+  // a later f3s_forward_status reads is cleared by the kernel itself.
+  if (blockIdx.x == 0 && threadIdx.x == 0) p.hdr[HDR_STATUS] = 0;
   trace_begin(p);
   const long long total = (long long)p.n_rw * p.heads;
   int round = 0;
@@ -888,39 +891,19 @@ struct KernelCfg {
   int path;
 };
 
-static int env_int(const char *name, int dflt) {
-  const char *e = getenv(name);
-  return e ? atoi(e) : dflt;
-}
-
 // Kernel choice per head dimension.  d = 64 defaults to the cp.async kernel with separate K and
-// V rings (measured fastest on B200).  Tuning knobs (environment, read once):
-//   F3S_FWD_PATH=cpasync | split | tma   data path for d = 64
-//   F3S_FWD_CFG=n                        alternative tile shapes of the plain cp.async kernel (d = 64)
-//   F3S_FWD_CFG32=1 / F3S_FWD_CFG128=1   the earlier tile shapes for d <= 32 / d > 64 (A/B runs)
+// V rings (measured fastest on B200).  F3S_FWD_PATH=cpasync | split | tma (environment, read once)
+// selects another data path for d = 64; the parity tests run every path.
 static KernelCfg kernel_cfg(int d) {
-  if (d == 32) {  // 16 warps with two stages beat 8 warps with four (0.48 vs 0.73 ms on a 29 M-edge graph)
-    static const int alt32 = env_int("F3S_FWD_CFG32", 0);
-    return alt32 == 1 ? KernelCfg{4, 4, 8, PATH_CPASYNC} : KernelCfg{4, 2, 16, PATH_CPASYNC};
-  }
-  if (d == 128) {  // 8 warps on 16-column steps beat 4 warps on 32-column steps (1.44 vs 1.65 ms, same graph)
-    static const int alt128 = env_int("F3S_FWD_CFG128", 0);
-    return alt128 == 1 ? KernelCfg{4, 3, 4, PATH_CPASYNC} : KernelCfg{2, 2, 8, PATH_CPASYNC};
-  }
+  if (d == 32) return {4, 2, 16, PATH_CPASYNC};  // 16 warps with two stages beat 8 warps with four
+  if (d == 128) return {2, 2, 8, PATH_CPASYNC};  // 8 warps on 16-column steps beat 4 warps on 32-column steps
   static const int path = [] {
     const char *e = getenv("F3S_FWD_PATH");
     if (e && strcmp(e, "cpasync") == 0) return (int)PATH_CPASYNC;
     if (e && strcmp(e, "tma") == 0) return (int)PATH_TMA;
     return (int)PATH_SPLIT;
   }();
-  static const int pick = env_int("F3S_FWD_CFG", 0);
-  if (path != PATH_CPASYNC) return {4, 2, 12, path};
-  switch (pick) {
-    case 1: return {4, 3, 8, PATH_CPASYNC};
-    case 2: return {2, 3, 12, PATH_CPASYNC};
-    case 3: return {2, 2, 16, PATH_CPASYNC};
-    default: return {4, 2, 12, PATH_CPASYNC};
-  }
+  return {4, 2, 12, path};
 }
 
 struct Geometry {
@@ -1000,7 +983,7 @@ static int launch(const FwdParams &p, bool softmax, int grid, cudaStream_t strea
     F3S_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     kern<<<grid, WARPS * 32, C::SMEM_BYTES, stream>>>(p);
   }
-  F3S_CUDA_TRY(cudaGetLastError());
+  F3S_CHECK_LAUNCH();
   return F3S_OK;
 }
 
@@ -1016,7 +999,7 @@ static int launch_coop(const FwdParams &p, bool softmax, int grid, cudaStream_t 
     F3S_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     kern<<<grid, WARPS * 32, C::SMEM_BYTES, stream>>>(p);
   }
-  F3S_CUDA_TRY(cudaGetLastError());
+  F3S_CHECK_LAUNCH();
   return F3S_OK;
 }
 
@@ -1059,9 +1042,8 @@ static int launch_tma(const FwdParams &p, bool softmax, int grid, cudaStream_t s
   // Q: exact row count, so that rows past the last node are zero-filled by the hardware.
   if (int rc = make_map(&tmq, p.q, p.ld, (unsigned long long)p.n_nodes, 64, 16)) return rc;
   // K, V: the row count is not an argument of the C ABI; every column id must have a row.
-  static const int box_rows = env_int("F3S_TMA_GATHER_BOX_ROWS", 1);
-  if (int rc = make_map(&tmk, p.k, p.ld, 1ull << 31, 64, box_rows)) return rc;
-  if (int rc = make_map(&tmv, p.v, p.ld, 1ull << 31, 64, box_rows)) return rc;
+  if (int rc = make_map(&tmk, p.k, p.ld, 1ull << 31, 64, 1)) return rc;
+  if (int rc = make_map(&tmv, p.v, p.ld, 1ull << 31, 64, 1)) return rc;
   const int smem = tma::smem_bytes(WARPS);
   if (softmax) {
     auto kern = fwd_kernel_tma<WARPS, true>;
@@ -1072,7 +1054,7 @@ static int launch_tma(const FwdParams &p, bool softmax, int grid, cudaStream_t s
     F3S_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     kern<<<grid, WARPS * 32, smem, stream>>>(p, tmq, tmk, tmv);
   }
-  F3S_CUDA_TRY(cudaGetLastError());
+  F3S_CHECK_LAUNCH();
   return F3S_OK;
 }
 
@@ -1088,7 +1070,7 @@ static int launch_split(const FwdParams &p, bool softmax, int grid, cudaStream_t
     F3S_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     kern<<<grid, WARPS * 32, C::SMEM_BYTES, stream>>>(p);
   }
-  F3S_CUDA_TRY(cudaGetLastError());
+  F3S_CHECK_LAUNCH();
   return F3S_OK;
 }
 
@@ -1102,6 +1084,11 @@ extern "C" size_t f3s_forward_workspace_bytes(int32_t n_row_windows, int64_t n_t
   if (!dim_supported(head_dim)) return 0;
   return geometry(n_row_windows, n_tcb, block_w, heads, head_dim).total_bytes;
 }
+
+// Testing aid: caps the capacity of the schedule's unit list (0 = no cap), so that the overflow report
+// of the schedule kernel can be exercised.  Process-wide.
+static int g_unit_list_limit = 0;
+extern "C" void f3s_debug_set_unit_list_limit(int32_t limit) { g_unit_list_limit = limit > 0 ? limit : 0; }
 
 // Validation + launch shared by the entry points.  budget_bytes > 0 lets the schedule use
 // fewer, larger chunks so that its scratch fits in that many bytes.
@@ -1132,7 +1119,8 @@ static int forward_impl(const int32_t *row_window_offset, const int32_t *sorted_
   auto misaligned = [](const void *ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) != 0; };
   F3S_REQUIRE(!misaligned(q) && !misaligned(k) && !misaligned(v) && !misaligned(out) && !misaligned(tcb_bitmap),
               F3S_ERR_INVALID_ARG, "q, k, v, out and tcb_bitmap must be 16-byte aligned");
-  const Geometry gm = geometry(n_row_windows, n_tcb, block_w, heads, head_dim, budget_bytes);
+  Geometry gm = geometry(n_row_windows, n_tcb, block_w, heads, head_dim, budget_bytes);
+  if (!gm.direct && g_unit_list_limit > 0 && gm.max_slots > g_unit_list_limit) gm.max_slots = g_unit_list_limit;
   F3S_REQUIRE(workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255) == 0, F3S_ERR_WORKSPACE,
               "workspace must be non-null and 256-byte aligned");
   F3S_REQUIRE(workspace_bytes >= gm.total_bytes, F3S_ERR_WORKSPACE, "workspace too small: %zu < %zu",
@@ -1178,17 +1166,14 @@ static int forward_impl(const int32_t *row_window_offset, const int32_t *sorted_
     plan_kernel<<<(n_row_windows + PLAN_THREADS - 1) / PLAN_THREADS, PLAN_THREADS, 0, stream>>>(
         row_window_offset, sorted_row_windows, n_row_windows, p.t8_per_tcb, gm.ch8, gm.kc.nt8, p.hdr,
         reinterpret_cast<UnitDesc *>(ws + gm.off_units), gm.max_slots);
-    F3S_CUDA_TRY(cudaGetLastError());
+    F3S_CHECK_LAUNCH();
   }
   const bool sm = apply_softmax != 0;
   const KernelCfg kc = gm.kc;
-  static const int coop_off = env_int("F3S_DIRECT_COOP", 1) == 0;  // 0: direct mode on the per-warp kernels (A/B)
-  if (gm.direct && !coop_off) {
+  if (gm.direct) {
 #define F3S_LAUNCH_COOP(D_, N_, S_, W_) \
   if (padded_dim(head_dim) == D_ && kc.nt8 == N_ && kc.stages == S_ && kc.warps == W_) return launch_coop<D_, N_, S_, W_>(p, sm, grid, stream)
-    F3S_LAUNCH_COOP(32, 4, 4, 8);
     F3S_LAUNCH_COOP(32, 4, 2, 16);
-    F3S_LAUNCH_COOP(128, 4, 3, 4);
     F3S_LAUNCH_COOP(128, 2, 2, 8);
     F3S_LAUNCH_COOP(64, 4, 2, 12);
 #undef F3S_LAUNCH_COOP
@@ -1200,14 +1185,9 @@ static int forward_impl(const int32_t *row_window_offset, const int32_t *sorted_
   }
 #define F3S_LAUNCH(D_, N_, S_, W_) \
   if (padded_dim(head_dim) == D_ && kc.nt8 == N_ && kc.stages == S_ && kc.warps == W_) return launch<D_, N_, S_, W_>(p, sm, grid, stream)
-  F3S_LAUNCH(32, 4, 4, 8);
   F3S_LAUNCH(32, 4, 2, 16);
-  F3S_LAUNCH(128, 4, 3, 4);
   F3S_LAUNCH(128, 2, 2, 8);
   F3S_LAUNCH(64, 4, 2, 12);
-  F3S_LAUNCH(64, 4, 3, 8);
-  F3S_LAUNCH(64, 2, 3, 12);
-  F3S_LAUNCH(64, 2, 2, 16);
 #undef F3S_LAUNCH
   set_error("no kernel instance for head_dim %d", head_dim);
   return F3S_ERR_UNSUPPORTED;
@@ -1263,6 +1243,33 @@ extern "C" int f3s_forward_traced(const int32_t *row_window_offset, const int32_
                       workspace, workspace_bytes, 0, sm_trace, nullptr, stream);
 }
 
+// Reads the status word the kernels of the last forward call on `workspace` left behind.
+extern "C" int f3s_forward_status(const void *workspace, int32_t *status_host, f3s_stream_t stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  F3S_REQUIRE(workspace != nullptr, F3S_ERR_INVALID_ARG, "null workspace");
+  const int *word = static_cast<const int *>(workspace) + HDR_STATUS;
+  if (status_host != nullptr) {  // non-blocking form: the caller synchronises and decodes
+    F3S_CUDA_TRY(cudaMemcpyAsync(status_host, word, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    return F3S_OK;
+  }
+  int st = 0;
+  F3S_CUDA_TRY(cudaMemcpyAsync(&st, word, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  F3S_CUDA_TRY(cudaStreamSynchronize(stream));
+  return f3s_status_word_to_code(st);
+}
+
+extern "C" int f3s_status_word_to_code(int32_t word) {
+  if (word == 0) return F3S_OK;
+  if (word == STATUS_LIST_OVERFLOW)
+    set_error("device status %d: the schedule's unit list overflowed; some row windows were not processed", word);
+  else if (word == STATUS_WAIT_TIMEOUT)
+    set_error("device status %d: a bounded wait for an asynchronous copy ran out; some row windows were not stored",
+              word);
+  else
+    set_error("device status %d: unknown", word);
+  return F3S_ERR_DEVICE;
+}
+
 // ---------------------------------------------------------------------------------------
 // Entry point for callers that must not allocate device memory.
 // ---------------------------------------------------------------------------------------
@@ -1315,4 +1322,11 @@ extern "C" int f3s_forward_static(const int32_t *row_window_offset, const int32_
   return forward_impl(row_window_offset, sorted_row_windows, sparse_a_to_x_idx, tcb_bitmap, num_nodes, n_row_windows,
                       n_tcb, block_w, heads, head_dim, ld, q, k, v, scale_divisor, apply_softmax, out, 0, nullptr,
                       scratch, F3S_STATIC_SCRATCH_BYTES, F3S_STATIC_SCRATCH_BYTES, nullptr, nullptr, stream);
+}
+
+// f3s_forward_status for the built-in scratch of f3s_forward_static (allocates nothing either).
+extern "C" int f3s_forward_static_status(int32_t *status_host, f3s_stream_t stream) {
+  void *scratch = nullptr;
+  if (int rc = static_scratch_ptr(&scratch)) return rc;
+  return f3s_forward_status(scratch, status_host, stream);
 }

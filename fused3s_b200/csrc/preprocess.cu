@@ -766,7 +766,8 @@ static int inclusive_scan_inplace(int *x, long long n, int *tile_sums, cudaStrea
   scan_tile_sums<<<n_tiles, SCAN_THREADS, 0, stream>>>(x, n, tile_sums);
   scan_sums<<<1, SCAN_THREADS, 0, stream>>>(tile_sums, n_tiles);
   scan_apply<<<n_tiles, SCAN_THREADS, 0, stream>>>(x, n, tile_sums);
-  F3S_CUDA_TRY(cudaGetLastError());
+  note_launches(2);
+  F3S_CHECK_LAUNCH();
   return F3S_OK;
 }
 
@@ -870,23 +871,31 @@ extern "C" int f3s_preprocess_count_rect(const int32_t *colidx, const int32_t *r
     window_rank_small<<<(n_rw + SW_WARPS - 1) / SW_WARPS, SW_WARPS * 32, 0, stream>>>(
         colidx, rowptr, num_nodes, n_rw, num_cols, block_w, block_partition, edge_to_column, edge_to_row, hdr,
         large_list);
-    F3S_CUDA_TRY(cudaGetLastError());
+    F3S_CHECK_LAUNCH();
     F3S_CUDA_TRY(cudaFuncSetAttribute(window_rank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, RANK_SMEM_BYTES));
     window_rank_kernel<<<min(n_rw, sm_count() * 3), WIN_THREADS, RANK_SMEM_BYTES, stream>>>(
         colidx, rowptr, num_nodes, num_cols, block_w, large_list, block_partition, edge_to_column, edge_to_row,
         reinterpret_cast<int *>(ws + L.off_a), reinterpret_cast<int *>(ws + L.off_b), hdr);
-    F3S_CUDA_TRY(cudaGetLastError());
+    F3S_CHECK_LAUNCH();
     copy_shifted<<<(n_rw + 255) / 256, 256, 0, stream>>>(block_partition, row_window_offset, n_rw);
-    F3S_CUDA_TRY(cudaGetLastError());
+    F3S_CHECK_LAUNCH();
     if (int rc = inclusive_scan_inplace(row_window_offset + 1, n_rw, reinterpret_cast<int *>(ws + L.off_sums), stream))
       return rc;
   } else {
     F3S_CUDA_TRY(cudaMemsetAsync(row_window_offset, 0, sizeof(int), stream));
   }
   int host_hdr[PH_INTS];
+  int scanned_total = 0;
   F3S_CUDA_TRY(cudaMemcpyAsync(host_hdr, hdr, sizeof(host_hdr), cudaMemcpyDeviceToHost, stream));
+  F3S_CUDA_TRY(cudaMemcpyAsync(&scanned_total, row_window_offset + n_rw, sizeof(int), cudaMemcpyDeviceToHost, stream));
   F3S_CUDA_TRY(cudaStreamSynchronize(stream));
   F3S_REQUIRE(host_hdr[PH_ERROR] == 0, F3S_ERR_INVALID_ARG, "colidx holds a value outside [0, %d)", num_cols);
+  // Windows without edges keep the caller's block_partition entry (as src/utils.cu:141-142 does), so a
+  // caller that did not zero the array gets offsets that disagree with the TCB count; every array sized
+  // by that count would then be overrun by the second phase.  Refuse instead.
+  F3S_REQUIRE(scanned_total == host_hdr[PH_SUM_TCB], F3S_ERR_INVALID_ARG,
+              "block_partition was not zeroed by the caller: its entries for row windows without edges add %d "
+              "TC blocks that do not exist", scanned_total - host_hdr[PH_SUM_TCB]);
   *n_tcb_host = host_hdr[PH_SUM_TCB];
   *max_tcb_per_window_host = host_hdr[PH_MAX_TCB];
   return F3S_OK;
@@ -932,19 +941,19 @@ extern "C" int f3s_preprocess_fill(const int32_t *colidx, const int32_t *rowptr,
       colidx, rowptr, num_nodes, n_rw, block_w, edge_to_column, edge_to_row, row_window_offset, tcblock_rowid,
       tcblocktile_id, tcblock_offset, sparse_a_to_x_idx, reinterpret_cast<unsigned long long *>(tcb_bitmap), hdr,
       large_list);
-  F3S_CUDA_TRY(cudaGetLastError());
+  F3S_CHECK_LAUNCH();
   F3S_CUDA_TRY(cudaFuncSetAttribute(window_fill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FILL_SMEM_BYTES));
   window_fill_kernel<<<min(n_rw, sm_count() * 2), FILL_THREADS, FILL_SMEM_BYTES, stream>>>(
       colidx, rowptr, num_nodes, n_rw, block_w, edge_to_column, edge_to_row, row_window_offset, large_list, hdr,
       tcblock_rowid, tcblocktile_id, tcblock_offset, sparse_a_to_x_idx,
       reinterpret_cast<unsigned long long *>(tcb_bitmap), reinterpret_cast<int *>(ws + L.off_a),
       reinterpret_cast<int *>(ws + L.off_b));
-  F3S_CUDA_TRY(cudaGetLastError());
+  F3S_CHECK_LAUNCH();
   if (int rc = inclusive_scan_inplace(tcblock_offset + 1, n_tcb, reinterpret_cast<int *>(ws + L.off_sums), stream))
     return rc;
   schedule_kernel<<<1, SCHED_THREADS, 0, stream>>>(row_window_offset, n_rw, sorted_row_windows,
                                                    reinterpret_cast<unsigned long long *>(ws + L.off_s0),
                                                    reinterpret_cast<unsigned long long *>(ws + L.off_s1));
-  F3S_CUDA_TRY(cudaGetLastError());
+  F3S_CHECK_LAUNCH();
   return F3S_OK;
 }

@@ -343,18 +343,36 @@ class ShardedTrainingAttention:
         full = torch.empty((s.padded_cols,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
         return all_gather_padded(send, full)
 
-    def forward(self, q_local, k_local, v_local, scale_divisor: float = 1.0):
-        k_full, v_full = self.fwd.gather_kv(k_local, v_local)
+    def forward_save(self, q_local, k_local, v_local, scale_divisor: float = 1.0):
+        """Forward pass that returns ``(out, saved)``; ``saved`` owns everything ``backward_from`` needs
+        (its gathered K/V are buffers of their own), so any number of forwards may be outstanding --
+        several layers sharing one graph, gradient accumulation, an inference call in between."""
+        k_full, v_full = self._gather(k_local), self._gather(v_local)
         out, lse = cabi.forward_lse(self.fwd.tcb, self.shard.num_rows, q_local, k_full, v_full, scale_divisor)
-        self._saved = (q_local, k_local, v_local, k_full, v_full, out, lse, float(scale_divisor))
-        return out
+        return out, (q_local, k_local, v_local, k_full, v_full, out, lse, float(scale_divisor))
 
-    def backward(self, d_out_local, grad_dtype=None):
+    def backward_from(self, saved, d_out_local, grad_dtype=None):
         """(dq, dk, dv) of this rank's rows for the upstream gradient of its output rows."""
-        q_local, k_local, v_local, k_full, v_full, out, lse, scale = self._saved
+        q_local, k_local, v_local, k_full, v_full, out, lse, scale = saved
         n = self.shard.num_rows
         do_h, stats = cabi.backward_prepare(out, lse, d_out_local)
         dq = cabi.backward_dq(self.fwd.tcb, n, q_local, k_full, v_full, do_h, stats, scale, grad_dtype)
         q_full, do_full, stats_full = self._gather(q_local), self._gather(do_h), self._gather(stats)
         dk, dv = cabi.backward_dkv(self.tcb_t, n, k_local, v_local, q_full, do_full, stats_full, scale, grad_dtype)
         return dq, dk, dv
+
+    def forward(self, q_local, k_local, v_local, scale_divisor: float = 1.0):
+        """One-slot convenience form: keeps what ``backward`` needs inside this object.  A second
+        ``forward`` before the matching ``backward`` is refused (it would replace the saved tensors and
+        the backward would silently use the wrong ones); use ``forward_save`` / ``backward_from`` for that."""
+        if self._saved is not None:
+            raise RuntimeError("ShardedTrainingAttention.forward called again before backward; use forward_save / "
+                               "backward_from to keep several forward passes outstanding")
+        out, self._saved = self.forward_save(q_local, k_local, v_local, scale_divisor)
+        return out
+
+    def backward(self, d_out_local, grad_dtype=None):
+        if self._saved is None:
+            raise RuntimeError("ShardedTrainingAttention.backward without a preceding forward")
+        saved, self._saved = self._saved, None
+        return self.backward_from(saved, d_out_local, grad_dtype)

@@ -34,6 +34,11 @@ typedef void *f3s_stream_t;
 /* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
 int f3s_version(void);
 
+/* Number of CUDA kernels this library has launched in this process so far (all entry points, all
+ * devices).  For benchmarks that report how many launches a timed region held.  No reference
+ * counterpart. */
+uint64_t f3s_kernel_launch_count(void);
+
 /* Text of the calling thread's most recent error ("" if none).
  * Replaces the reference's printf + exit(-1) error path (src/F3S_kernel.cu:662-666,
  * src/utils.cu:73-77). */
@@ -169,6 +174,46 @@ int f3s_forward_traced(const int32_t *row_window_offset, const int32_t *sorted_r
                        uint64_t *sm_trace, f3s_stream_t stream);
 
 /*
+ * Device-side error reporting.  The reference's kernels report nothing and its host code ends the
+ * process on any CUDA error (printf + exit(-1), src/F3S_kernel.cu:662-666); here a kernel that cannot
+ * finish its work writes a status word into the scratch of the call and returns, and the host reads it.
+ *
+ * f3s_forward_status: status of the most recent f3s_forward / _f16out / _lse / _traced call that used
+ *   `workspace`, issued on `stream`.
+ *     status_host == NULL: blocks until the stream has drained, returns F3S_OK or F3S_ERR_DEVICE
+ *       (text through f3s_last_error_string): the schedule's unit list overflowed, or a bounded wait
+ *       for an asynchronous copy ran out -- in both cases some output rows were not written.
+ *     status_host != NULL (HOST pointer, pinned for a truly asynchronous copy): enqueues a 4-byte copy
+ *       of the raw word and returns at once; after synchronising, f3s_status_word_to_code(*status_host)
+ *       gives the same code and text.
+ * f3s_forward_static_status: the same for the built-in scratch of f3s_forward_static.
+ * f3s_debug_set_unit_list_limit: testing aid without effect on results in normal use -- caps the
+ *   capacity of the schedule's unit list (0 removes the cap) so that the overflow report can be
+ *   exercised by a test; with a cap in place heavy row windows may be left unprocessed and the status
+ *   call says so.
+ */
+int f3s_forward_status(const void *workspace, int32_t *status_host, f3s_stream_t stream);
+int f3s_forward_static_status(int32_t *status_host, f3s_stream_t stream);
+int f3s_status_word_to_code(int32_t word);
+void f3s_debug_set_unit_list_limit(int32_t limit);
+
+/*
+ * Checks every index of a plan that the forward and backward kernels dereference without a test of
+ * their own: row_window_offset starts at 0, never decreases and ends at n_tcb; every entry of
+ * sorted_row_windows (may be NULL) lies in [0, n_row_windows); every column id of sparse_a_to_x_idx
+ * lies in [0, num_kv_rows), the row count of the K / V tensors the plan will be used with.  Plans made
+ * by f3s_preprocess_* satisfy this by construction (columns are range-checked there); plans read from
+ * a file or assembled from parts should be checked once before their first use.  Blocks until the
+ * answer is known.  Returns F3S_OK, or F3S_ERR_INVALID_ARG with the first violation in the error text.
+ *   workspace: 16 bytes of device scratch, 16-byte aligned.
+ * The reference has no such check (its kernels index K and V with whatever the plan holds,
+ * src/F3S_kernel.cu:1652-1662).
+ */
+int f3s_validate_plan(const int32_t *row_window_offset, const int32_t *sorted_row_windows,
+                      const int32_t *sparse_a_to_x_idx, int32_t n_row_windows, int64_t n_tcb, int32_t block_w,
+                      int32_t num_kv_rows, void *workspace, size_t workspace_bytes, f3s_stream_t stream);
+
+/*
  * Training support.  The reference is inference-only (src/F3S.cpp:298-305 exports forward ops and
  * no gradient); these three entry points have no reference counterpart.
  *
@@ -275,6 +320,17 @@ int f3s_forward_static(const int32_t *row_window_offset, const int32_t *sorted_r
                        int32_t n_row_windows, int64_t n_tcb, int32_t block_w, int32_t heads, int32_t head_dim,
                        int64_t ld, const void *q, const void *k, const void *v, float scale_divisor,
                        int32_t apply_softmax, float *out, f3s_stream_t stream);
+
+/* ------------------------------------------------------------------------------------
+ * Measurement aid (no reference counterpart): gathers n_ids rows of 128 bytes from `table`
+ * (table_rows rows, 16-byte aligned) at the row ids given (each in [0, table_rows); not checked) and
+ * discards them -- loads only, eight 16-byte loads in flight per thread.  Timed by the caller with
+ * events on `stream`, 128 * n_ids bytes / time is the gather rate this GPU can sustain from L2 (table
+ * smaller than L2) or from HBM (larger): the ceiling for the fused kernel's K / V row gathers.
+ * n_ids is rounded down to a multiple of 32.  sink: 4 bytes of device memory (never written in practice).
+ * ------------------------------------------------------------------------------------ */
+int f3s_probe_gather_rows(const void *table, int64_t table_rows, const int32_t *row_ids, int64_t n_ids, void *sink,
+                          f3s_stream_t stream);
 
 /* ------------------------------------------------------------------------------------
  * Multi-GPU planning (host only, no device work): cut points of a contiguous row-window

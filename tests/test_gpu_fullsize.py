@@ -23,7 +23,7 @@ DEV = "cuda:0"
 def problem():
     from fused3s_b200 import cabi
 
-    g = graphs.make_config(4, scale=1.0)
+    g = graphs.make_config(4, device=DEV, scale=1.0)  # integer steps on the device: same arrays as on the host
     q, k, v = graphs.make_features(g)
     rp, ci = torch.from_numpy(g.rowptr).to(DEV), torch.from_numpy(g.colidx).to(DEV)
     tcb = cabi.preprocess(ci, rp, g.num_nodes, 16)
@@ -63,6 +63,43 @@ def test_fullsize_preprocessing_round_trip(problem):
     deg = (rp[1:] - rp[:-1]).long()
     want = torch.repeat_interleave(torch.arange(n, device=DEV), deg) * n + ci.long()  # rows ascend, columns ascend
     assert keys.numel() == nnz and torch.equal(keys, want)
+
+
+def ref_preprocess_equal(mod, rp, ci, n, tcb):
+    """All ten arrays of ``tcb`` against the rebuilt reference's preprocess_gpu on the same CSR, on the
+    device (bit for bit).  The reference prints from C; that goes to this process's stdout as it does there."""
+    nnz = ci.numel()
+    nrw = (n + 15) // 16
+    bp = torch.zeros(nrw, dtype=torch.int32, device=DEV)
+    e2c = torch.zeros(nnz, dtype=torch.int32, device=DEV)
+    e2r = torch.zeros(nnz, dtype=torch.int32, device=DEV)
+    res = mod.preprocess_gpu(ci, rp, n, 16, 16, bp, e2c, e2r)
+    torch.cuda.synchronize()
+    names = ["rowWindowOffset", "sortedRowWindows", "tcblock_rowid", "tcblocktile_id", "tcblock_offset",
+             "sparseAToXidx", "tcbBitMap"]
+    assert int(res[7]) == tcb["nTCB"]
+    for name, want in zip(names, res[:7]):
+        got = tcb[name]
+        assert got.shape == want.shape and got.element_size() == want.element_size(), name
+        if name == "tcbBitMap":
+            got, want = got.view(torch.int64), want.view(torch.int64)
+        assert got.dtype == want.dtype and torch.equal(got, want), f"{name} differs from the rebuilt reference"
+    for name, want in (("blockPartition", bp), ("edgeToColumn", e2c), ("edgeToRow", e2r)):
+        assert torch.equal(tcb[name], want), f"{name} differs from the rebuilt reference"
+
+
+def test_fullsize_tcb_arrays_bit_exact_against_rebuilt_reference(problem):
+    """The reference's own preprocessing (src/F3S.cpp:40-87), rebuilt for sm_100a with the one-token
+    repair of its edgeToRow stride (src/utils.cu:348; rows of degree > 32 need it), on the 115 M-edge CSR:
+    every array of the tuple and the three in-place outputs must be equal bit for bit.  This is where the
+    large-window paths run (global-scratch sort above 4 096 edges, multi-pass fill above 16 384)."""
+    from oracle import build_ref
+
+    fix = build_ref.load("F3S_ref_rowfix")
+    if fix is None:
+        pytest.skip("oracle/_ref not built")
+    g, _, _, _, rp, ci, tcb = problem
+    ref_preprocess_equal(fix, rp, ci, g.num_nodes, tcb)
 
 
 def test_fullsize_forward_properties_and_sampled_parity(problem):

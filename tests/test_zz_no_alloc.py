@@ -41,6 +41,8 @@ def test_static_scratch_forward_matches_workspace_forward_twice():
     n, rowptr, colidx, q, k, v = _problem()
     tcb = cabi.preprocess(torch.from_numpy(colidx).to(DEV), torch.from_numpy(rowptr).to(DEV), n, 16)
     qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    ws_bytes = cabi.lib().f3s_forward_workspace_bytes(tcb["rowWindowOffset"].numel() - 1, tcb["nTCB"], 16, 1, 64)
+    assert 256 < ws_bytes <= cabi.STATIC_SCRATCH_BYTES  # scheduled mode (schedule + partials in scratch), no growth
     want = cabi.forward(tcb, n, qd, kd, vd, 8.0)  # the existing entry point, caller-provided workspace
     oracle = ao.edge_attention(rowptr, colidx, q, k, v, scale_divisor=8.0)
     out = torch.empty_like(want)  # every buffer is allocated before the calls under test
@@ -62,6 +64,48 @@ def test_static_scratch_forward_matches_workspace_forward_twice():
     cabi.forward_static(tcb2, g.num_nodes, q2.to(DEV), k2.to(DEV), v2.to(DEV), out2, 8.0)
     torch.cuda.synchronize()
     assert torch.allclose(out2, want2, rtol=1e-4, atol=1e-5)
+
+
+def test_static_scratch_with_chunks_grown_to_fit_and_without_any_allocation():
+    """A graph whose schedule would need 87 MB with the usual chunk size: the entry point has to grow
+    the chunks of heavy row windows (twice) until the scratch fits its 32 MiB, a geometry that
+    ``f3s_forward`` never uses for this problem.  Also checks what the entry point is for: the device's
+    free memory is the same before and after a call."""
+    from fused3s_b200 import cabi
+
+    n, d = 32768, 64
+    rowptr, colidx = graphs.chung_lu(n, 6_000_000, 2.1, 4000, seed=11, device=DEV)
+    gen = torch.Generator().manual_seed(13)
+    q, k, v = (torch.randn(n, d, generator=gen).half() for _ in range(3))
+    tcb = cabi.preprocess(torch.from_numpy(colidx).to(DEV), torch.from_numpy(rowptr).to(DEV), n, 16)
+    ws_bytes = cabi.lib().f3s_forward_workspace_bytes(tcb["rowWindowOffset"].numel() - 1, tcb["nTCB"], 16, 1, d)
+    assert ws_bytes > cabi.STATIC_SCRATCH_BYTES, "the case must not fit without growing the chunks"
+    qd, kd, vd = q.to(DEV), k.to(DEV), v.to(DEV)
+    want = cabi.forward(tcb, n, qd, kd, vd, 8.0)
+    oracle = ao.edge_attention(rowptr, colidx, q, k, v, scale_divisor=8.0)
+    out = torch.empty_like(want)
+    cabi.forward_static(tcb, n, qd, kd, vd, out, 8.0)  # first call on the device: looks up the array's address
+    torch.cuda.synchronize()
+    for call in range(2):
+        out.fill_(float("nan"))
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info(torch.device(DEV))[0]
+        cabi.forward_static(tcb, n, qd, kd, vd, out, 8.0)
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info(torch.device(DEV))[0] == free_before, "the call changed the free device memory"
+        cabi.forward_static_status(DEV)
+        assert torch.isfinite(out).all(), f"call {call}"
+        assert torch.allclose(out, want, rtol=1e-4, atol=1e-5), f"call {call} differs from f3s_forward"
+        m = ao.compare(out.cpu(), oracle)
+        assert m["max_abs"] <= ao.MAX_ABS_TOL and m["mean_rel"] <= ao.MEAN_REL_TOL, (call, m)
+    # strided views (the three slices of one fused projection buffer) are read with their real row stride
+    qkv = torch.stack([qd, kd, vd], dim=1).contiguous()  # [N, 3, d]
+    out.fill_(float("nan"))
+    cabi.forward_static(tcb, n, qkv[:, 0], qkv[:, 1], qkv[:, 2], out, 8.0)
+    torch.cuda.synchronize()
+    assert torch.allclose(out, want, rtol=1e-4, atol=1e-5)
+    with pytest.raises(cabi.F3SError):  # a wrong output buffer is refused before anything is launched
+        cabi.forward_static(tcb, n, qd, kd, vd, torch.empty(n, d, dtype=torch.float16, device=DEV), 8.0)
 
 
 def test_static_scratch_rejects_oversized_problem():
