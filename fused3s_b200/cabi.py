@@ -34,6 +34,11 @@ EXPORTS = (
     "f3s_forward_static",
     "f3s_forward_traced",
     "f3s_forward_lse",
+    "f3s_forward_plan",
+    "f3s_forward_planned",
+    "f3s_forward_phased_workspace_bytes",
+    "f3s_forward_phased_plan",
+    "f3s_forward_phase",
     "f3s_forward_status",
     "f3s_forward_static_status",
     "f3s_status_word_to_code",
@@ -98,6 +103,18 @@ def lib() -> C.CDLL:
         l.f3s_forward_lse.restype = C.c_int
         l.f3s_forward_lse.argtypes = [vp, vp, vp, vp, i32, i32, i64, i32, i32, i32, i64, vp, vp, vp, f32, vp, vp, vp,
                                       sz, vp]
+        l.f3s_forward_plan.restype = C.c_int
+        l.f3s_forward_plan.argtypes = [vp, vp, i32, i32, i64, i32, i32, i32, vp, sz, vp]
+        l.f3s_forward_planned.restype = C.c_int
+        l.f3s_forward_planned.argtypes = [vp, vp, vp, vp, i32, i32, i64, i32, i32, i32, i64, vp, i64, vp, vp, f32, i32,
+                                          vp, i32, vp, sz, vp]
+        l.f3s_forward_phased_workspace_bytes.restype = sz
+        l.f3s_forward_phased_workspace_bytes.argtypes = [i32, i64, i32, i32, i32]
+        l.f3s_forward_phased_plan.restype = C.c_int
+        l.f3s_forward_phased_plan.argtypes = [vp, vp, vp, i32, i32, i64, i32, i32, i32, vp, sz, vp]
+        l.f3s_forward_phase.restype = C.c_int
+        l.f3s_forward_phase.argtypes = [i32, vp, vp, vp, vp, vp, i32, i32, i32, i64, i32, i32, i32, i64, vp, i64, vp,
+                                        vp, f32, vp, vp, sz, vp]
         l.f3s_forward_status.restype = C.c_int
         l.f3s_forward_status.argtypes = [vp, vp, vp]
         l.f3s_forward_static_status.restype = C.c_int
@@ -209,15 +226,18 @@ class ForwardPlan:
         self.num_nodes = num_nodes
         self.tcb = tcb
         self.q, self.k, self.v = q, k, v
-        # Row stride in elements.  Q, K and V may be views into one buffer (for instance the three
-        # slices of a fused QKV projection output [N, 3*H*d]) as long as each row's heads*d values are
-        # contiguous and the three views share the row stride.
-        self.ld = int(q.stride(0)) if q.shape[0] > 1 else self.heads * self.dim
-        for name, t in (("q", q), ("k", k), ("v", v)):
+        # Row strides in elements.  Q, K and V may be views into larger buffers (the three slices of a fused
+        # QKV projection output, or K and V rows interleaved in one gathered buffer) as long as each row's
+        # heads*d values are contiguous; K and V share one row stride, Q has its own.
+        def row_stride(t):
+            return int(t.stride(0)) if t.shape[0] > 1 else self.heads * self.dim
+
+        self.ld, self.ld_kv = row_stride(q), row_stride(k)
+        for name, t, ld in (("q", q, self.ld), ("k", k, self.ld_kv), ("v", v, self.ld_kv)):
             inner_ok = t.stride(-1) == 1 and (t.dim() == 2 or t.stride(1) == self.dim)
-            row_ok = t.shape[0] <= 1 or t.stride(0) == self.ld
-            if not (inner_ok and row_ok and self.ld >= self.heads * self.dim):
-                raise F3SError(ERR_INVALID_ARG, f"{name}: rows must be contiguous and share one row stride")
+            row_ok = t.shape[0] <= 1 or t.stride(0) == ld
+            if not (inner_ok and row_ok and ld >= self.heads * self.dim):
+                raise F3SError(ERR_INVALID_ARG, f"{name}: rows must be contiguous; k and v must share one row stride")
         self.block_w = tcb["block_w"]
         self.n_rw = tcb["rowWindowOffset"].numel() - 1
         self.n_tcb = tcb["sparseAToXidx"].numel() // self.block_w
@@ -236,10 +256,27 @@ class ForwardPlan:
         if self.ws_bytes == 0:
             raise F3SError(ERR_UNSUPPORTED, f"unsupported head_dim {self.dim} / block_w {self.block_w}")
         self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=self.dev)
+        self.planned = False  # the schedule is written into the scratch by the first launch
 
     def launch(self, stream=None) -> None:
         s = _stream(self.dev) if stream is None else C.c_void_p(stream)
         t = self.tcb
+        if self.sddmm is None:
+            # schedule once (first launch, same stream), then one kernel per call
+            if not self.planned:
+                check(self.l.f3s_forward_plan(_ptr(t["rowWindowOffset"]), _ptr(self.sorted), self.num_nodes, self.n_rw,
+                                              self.n_tcb, self.block_w, self.heads, self.dim, _ptr(self.ws),
+                                              self.ws_bytes, s))
+                self.planned = True
+            check(self.l.f3s_forward_planned(_ptr(t["rowWindowOffset"]), _ptr(self.sorted), _ptr(t["sparseAToXidx"]),
+                                             _ptr(t["tcbBitMap"]), self.num_nodes, self.n_rw, self.n_tcb,
+                                             self.block_w, self.heads, self.dim, self.ld, _ptr(self.q), self.ld_kv,
+                                             _ptr(self.k), _ptr(self.v), self.scale_divisor, self.apply_softmax,
+                                             _ptr(self.out), 1 if self.out_half else 0, _ptr(self.ws), self.ws_bytes,
+                                             s))
+            return
+        if self.ld_kv != self.ld:
+            raise F3SError(ERR_INVALID_ARG, "the score dump needs q, k and v with one common row stride")
         if self.out_half:  # fp16 output entry point (no score dump)
             check(self.l.f3s_forward_f16out(_ptr(t["rowWindowOffset"]), _ptr(self.sorted), _ptr(t["sparseAToXidx"]),
                                             _ptr(t["tcbBitMap"]), self.num_nodes, self.n_rw, self.n_tcb, self.block_w,
@@ -258,7 +295,96 @@ class ForwardPlan:
         """Blocks until the plan's stream has drained and raises ``F3SError`` (``ERR_DEVICE``) if a
         kernel of the last launch reported that it could not finish (``f3s_forward_status``)."""
         s = _stream(self.dev) if stream is None else C.c_void_p(stream)
-        check(self.l.f3s_forward_status(_ptr(self.ws), None, s))
+        try:
+            check(self.l.f3s_forward_status(_ptr(self.ws), None, s))
+        except F3SError:
+            self.planned = False  # a failed launch may leave counters behind: schedule again before the next one
+            raise
+
+
+def phase_split_array(tcb: dict, col_split: int):
+    """For every row window the index of its first TC block whose first column id is >= ``col_split``
+    (``rowWindowOffset[w+1]`` if none): the ``phase_split`` argument of the two-phase entry points.
+    Integer bookkeeping on the plan's device, once per graph."""
+    import torch
+
+    bw = tcb["block_w"]
+    rwo = tcb["rowWindowOffset"].long()
+    first = tcb["sparseAToXidx"][::bw]  # a block's first slot is never padding
+    low = torch.zeros(first.numel() + 1, dtype=torch.int64, device=first.device)
+    low[1:] = torch.cumsum((first < col_split).to(torch.int64), 0)
+    # inside a window the blocks' first columns ascend, so the blocks below the split are a prefix
+    return (rwo[:-1] + (low[rwo[1:]] - low[rwo[:-1]])).to(torch.int32)
+
+
+class PhasedForwardPlan:
+    """Two-phase forward (``f3s_forward_phase``) of one problem: ``launch_phase(1)`` works on the columns
+    with id >= ``col_split`` and may run before the other K / V rows have arrived, ``launch_phase(2)`` does
+    the rest and writes ``out``.  head_dim 64, softmax always."""
+
+    def __init__(self, tcb: dict, num_nodes: int, q, k, v, scale_divisor: float, col_split: int, scheduled: bool = True,
+                 out=None):
+        import torch
+
+        self.l = lib()
+        self.dev = q.device
+        self.heads = q.shape[1] if q.dim() == 3 else 1
+        self.dim = q.shape[-1]
+        self.num_nodes, self.tcb, self.q, self.k, self.v = num_nodes, tcb, q, k, v
+        self.ld = _ld(q, self.heads, self.dim)
+        self.ld_kv = _ld(k, self.heads, self.dim)
+        if _ld(v, self.heads, self.dim) != self.ld_kv:
+            raise F3SError(ERR_INVALID_ARG, "k and v must share one row stride")
+        self.block_w = tcb["block_w"]
+        self.n_rw = tcb["rowWindowOffset"].numel() - 1
+        self.n_tcb = tcb["sparseAToXidx"].numel() // self.block_w
+        self.scale_divisor = float(scale_divisor)
+        self.col_split = int(col_split)
+        self.sorted = tcb["sortedRowWindows"] if scheduled else None
+        with torch.cuda.device(self.dev):
+            self.split = phase_split_array(tcb, self.col_split)
+            shape = (num_nodes,) + tuple(q.shape[1:])
+            self.out = torch.empty(shape, dtype=torch.float32, device=self.dev) if out is None else out
+            self.ws_bytes = self.l.f3s_forward_phased_workspace_bytes(self.n_rw, self.n_tcb, self.block_w, self.heads,
+                                                                      self.dim)
+            if self.ws_bytes == 0:
+                raise F3SError(ERR_UNSUPPORTED, f"two-phase calls need head_dim 64, got {self.dim}")
+            self.ws = torch.empty(self.ws_bytes, dtype=torch.uint8, device=self.dev)
+            check(self.l.f3s_forward_phased_plan(_ptr(tcb["rowWindowOffset"]), _ptr(self.sorted), _ptr(self.split),
+                                                 num_nodes, self.n_rw, self.n_tcb, self.block_w, self.heads, self.dim,
+                                                 _ptr(self.ws), self.ws_bytes, _stream(self.dev)))
+
+    def launch_phase(self, phase: int, stream=None) -> None:
+        s = _stream(self.dev) if stream is None else C.c_void_p(stream)
+        t = self.tcb
+        check(self.l.f3s_forward_phase(phase, _ptr(t["rowWindowOffset"]), _ptr(self.sorted), _ptr(t["sparseAToXidx"]),
+                                       _ptr(t["tcbBitMap"]), _ptr(self.split), self.col_split, self.num_nodes,
+                                       self.n_rw, self.n_tcb, self.block_w, self.heads, self.dim, self.ld,
+                                       _ptr(self.q), self.ld_kv, _ptr(self.k), _ptr(self.v), self.scale_divisor,
+                                       _ptr(self.out), _ptr(self.ws), self.ws_bytes, s))
+
+
+def window_tcb_counts(colidx, rowptr, num_nodes: int, block_w: int = 16):
+    """TC blocks per row window (int32 device tensor) without building the plan: the counting half of the
+    preprocessing (``f3s_preprocess_count``).  What a TCB-balanced partition of the windows is cut from."""
+    import torch
+
+    l = lib()
+    dev = colidx.device
+    nnz = int(colidx.numel())
+    n_rw = (num_nodes + 15) // 16
+    with torch.cuda.device(dev):
+        bp = torch.zeros(n_rw, dtype=torch.int32, device=dev)
+        e2c = torch.empty(nnz, dtype=torch.int32, device=dev)
+        e2r = torch.empty(nnz, dtype=torch.int32, device=dev)
+        rwo = torch.empty(n_rw + 1, dtype=torch.int32, device=dev)
+        ws_bytes = l.f3s_preprocess_workspace_bytes(num_nodes, nnz, block_w)
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+        n_tcb, max_tcb = C.c_int32(0), C.c_int32(0)
+        check(l.f3s_preprocess_count(_ptr(colidx), _ptr(rowptr), num_nodes, nnz, 16, block_w, _ptr(bp), _ptr(e2c),
+                                     _ptr(e2r), _ptr(rwo), _ptr(ws), ws_bytes, C.byref(n_tcb), C.byref(max_tcb),
+                                     _stream(dev)))
+    return bp
 
 
 def validate_plan(tcb: dict, num_kv_rows: int, scheduled: bool = True) -> None:

@@ -17,7 +17,9 @@ struct UnitDesc {        // 32 bytes
 
 // Header of the scratch area.  U_HEAVY: units in the list (chunks of heavy windows);
 // LIGHT_INV: n_rw - (first position in the window order that holds a light window).
-enum { HDR_U_HEAVY = 0, HDR_LIGHT_INV = 1, HDR_COUNTER = 2, HDR_STATUS = 3, HDR_INTS = 16 };
+// COUNTER: next position of the work order; DONE: warps that have run out of work (the last of them
+// resets both, so that a launch leaves the scratch ready for the next one).
+enum { HDR_U_HEAVY = 0, HDR_LIGHT_INV = 1, HDR_COUNTER = 2, HDR_STATUS = 3, HDR_DONE = 4, HDR_INTS = 16 };
 enum { STATUS_LIST_OVERFLOW = 1, STATUS_WAIT_TIMEOUT = 2 };
 
 struct FwdParams {
@@ -32,7 +34,8 @@ struct FwdParams {
   float *lse;     // may be null: [n_nodes][heads] log2-domain log-sum-exp of the scaled scores of every row
   int n_nodes, n_rw, heads;
   int d_real;     // head dimension of the tensors; the kernels' D is d_real rounded up to 32, 64 or 128
-  long long ld;  // row stride of q/k/v in elements
+  long long ld;     // row stride of q in elements
+  long long ld_kv;  // row stride of k and v in elements
   int t8_per_tcb;
   int direct;    // 1: no schedule, static round-robin over windows
   int ch8;       // windows with more tiles than this are processed as chunks from the list
@@ -44,7 +47,25 @@ struct FwdParams {
   float *partial;
   int max_slots;
   unsigned long long *sm_trace;  // may be null: [F3S_SM_TRACE_SLOTS][2] first-start / last-end ns per SM
+  // Two-phase calls (row-sharded attention that starts on the columns it already holds while the others
+  // are still in flight).  phase 0: the whole window.  phase 1: only columns with id >= col_split; the
+  // unnormalised result (running max, running sum, accumulator) goes to state[] instead of the output.
+  // phase 2: only columns with id < col_split, continuing from state[]; writes the output.
+  // phase_split[w]: first TC block of window w whose first column id is >= col_split (rwo[w+1] if none),
+  // so the block before it is the only one that can hold columns of both kinds.
+  int phase, col_split;
+  const int *phase_split;
+  float *state;  // [heads][n_rw] slots in the layout of a partial
 };
+
+// TC-block range of window w that a launch works on (see FwdParams::phase).
+template <class P>
+__device__ __forceinline__ void window_blocks(const P &p, int w, int &a, int &z) {
+  a = p.rwo[w];
+  z = p.rwo[w + 1];
+  if (p.phase == 1) a = max(a, p.phase_split[w] - 1);
+  else if (p.phase == 2) z = min(z, p.phase_split[w]);
+}
 
 constexpr unsigned FULL = 0xffffffffu;
 constexpr float NEG_INF = -INFINITY;
@@ -82,8 +103,14 @@ __device__ __forceinline__ void trace_end(const FwdParams &p, int lane) {
 // ---------------------------------------------------------------------------------------
 constexpr int PLAN_THREADS = 256;
 
+struct PlanArgs {  // the members window_blocks reads
+  const int *rwo;
+  int phase;
+  const int *phase_split;
+};
+
 static __global__ void __launch_bounds__(PLAN_THREADS)
-plan_kernel(const int *__restrict__ rwo, const int *__restrict__ sorted, int n_rw, int t8_per_tcb, int ch8,
+plan_kernel(const PlanArgs pa, const int *__restrict__ sorted, int n_rw, int t8_per_tcb, int ch8,
             int nt8, int *hdr, UnitDesc *units, int max_units) {
   const int i = blockIdx.x * PLAN_THREADS + threadIdx.x;
   const int lane = threadIdx.x & 31;
@@ -91,7 +118,8 @@ plan_kernel(const int *__restrict__ rwo, const int *__restrict__ sorted, int n_r
   bool heavy = false;
   if (i < n_rw) {
     w = sorted ? sorted[i] : i;
-    const int a = rwo[w], b = rwo[w + 1];
+    int a, b;
+    window_blocks(pa, w, a, b);
     first = a * t8_per_tcb;
     n8 = (b - a) * t8_per_tcb;
     heavy = n8 > ch8;
@@ -218,13 +246,29 @@ struct UnitSource {
       }
       const int i = first_light + (uu - u_heavy);
       u.window = p.sorted ? p.sorted[i] : i;
-      u.t8b = p.rwo[u.window] * p.t8_per_tcb;
-      u.t8e = p.rwo[u.window + 1] * p.t8_per_tcb;
+      int a, z;
+      window_blocks(p, u.window, a, z);
+      u.t8b = a * p.t8_per_tcb;
+      u.t8e = z * p.t8_per_tcb;
       if (p.direct || u.t8e - u.t8b <= p.ch8) return true;
       // a heavy window behind the first light one (window order not descending): it is in the list
     }
   }
 };
+
+// Called once by every warp of a scheduled launch after its last unit: the last warp to get here puts
+// the work counter back to zero, so the scratch can serve the next launch without a memset (every warp
+// has stopped drawing from the counter by then).
+template <class P>
+__device__ __forceinline__ void retire_warp(const P &p, int lane, int total_warps) {
+  if (p.direct || lane != 0) return;
+  __threadfence();
+  if (atomicAdd(&p.hdr[HDR_DONE], 1) == total_warps - 1) {
+    p.hdr[HDR_COUNTER] = 0;
+    p.hdr[HDR_DONE] = 0;
+    __threadfence();
+  }
+}
 
 // The same iterator for kernels that mostly see short windows (a step or two).  There the chain
 // counter -> window order -> window offsets, three dependent global loads, dominates a unit, so a
@@ -278,8 +322,10 @@ struct BatchedUnitSource {
     }
     const int i = first_light + (uu - u_heavy);
     u.window = p.sorted ? p.sorted[i] : i;
-    u.t8b = p.rwo[u.window] * p.t8_per_tcb;
-    u.t8e = p.rwo[u.window + 1] * p.t8_per_tcb;
+    int a, z;
+    window_blocks(p, u.window, a, z);
+    u.t8b = a * p.t8_per_tcb;
+    u.t8e = z * p.t8_per_tcb;
     if (!p.direct && u.t8e - u.t8b > p.ch8) u.window = -1;
   }
 

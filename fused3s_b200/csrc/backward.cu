@@ -47,6 +47,8 @@ struct BwdParams {
   void *out1, *out2;    // [n_nodes][heads][d_real]; out2 only in the dK/dV launch
   int out_half;         // 1: gradients are stored as fp16
   int fpart;            // which part of the feature columns this launch accumulates (FSPLIT > 1)
+  int phase;            // always 0 here: the backward works on whole windows (the shared iterator reads it)
+  const int *phase_split;
 };
 
 template <int D, int NT8, int STAGES, int WARPS>
@@ -431,6 +433,8 @@ static int run_bwd(BwdParams p, const BwdSched &sc, unsigned char *ws, const Bwd
   p.arrive = reinterpret_cast<int *>(ws + sc.off_arrive);
   p.partial = reinterpret_cast<float *>(ws + sc.off_partial);
   p.max_slots = sc.max_slots;
+  p.phase = 0;
+  p.phase_split = nullptr;
   const int warps = dkv ? kc.warps_dkv : kc.warps_dq;
   const int parts = dkv ? kc.fsplit : 1;
   for (int part = 0; part < parts; ++part) {
@@ -443,7 +447,7 @@ static int run_bwd(BwdParams p, const BwdSched &sc, unsigned char *ws, const Bwd
     } else {
       F3S_CUDA_TRY(cudaMemsetAsync(ws + sc.off_hdr, 0, sc.zero_bytes, stream));
       plan_kernel<<<(p.n_rw + PLAN_THREADS - 1) / PLAN_THREADS, PLAN_THREADS, 0, stream>>>(
-          p.rwo, p.sorted, p.n_rw, p.t8_per_tcb, sc.ch8, kc.nt8, p.hdr, reinterpret_cast<UnitDesc *>(ws + sc.off_units),
+          PlanArgs{p.rwo, 0, nullptr}, p.sorted, p.n_rw, p.t8_per_tcb, sc.ch8, kc.nt8, p.hdr, reinterpret_cast<UnitDesc *>(ws + sc.off_units),
           sc.max_slots);
       F3S_CHECK_LAUNCH();
     }

@@ -43,28 +43,30 @@ namespace f3s {
 
 // Mask the score tiles by the bitmap, update the online softmax, O += P V (V rows at vsm).
 // s is consumed (overwritten by the probabilities).
-template <int D, int NT8, bool SOFTMAX, bool CHECK_TAIL, bool SDDMM = true>
+// FILTER: additionally mask by cm, one bit per gathered column of the step (set = column takes part).
+template <int D, int NT8, bool SOFTMAX, bool CHECK_TAIL, bool SDDMM = true, bool FILTER = false>
 __device__ __forceinline__ void softmax_pv(const FwdParams &p, float (&s)[NT8][4], uint32_t vsm, const uint32_t *bm32,
                                            int n_valid, int t8_first, float (&o)[D / 8][4], float (&m_run)[2],
-                                           float (&l_run)[2], int lane, int bm_shift);
+                                           float (&l_run)[2], int lane, int bm_shift, uint32_t cm = 0xffffffffu);
 
 // One step of the fused loop on tiles already in shared memory: S = Q K^T, mask, online
 // softmax, O += P V.  n_valid (warp-uniform) = tiles of this step that belong to the unit;
 // CHECK_TAIL is set when stale bitmap words may sit behind them.
-template <int D, int NT8, bool SOFTMAX, bool CHECK_TAIL>
+template <int D, int NT8, bool SOFTMAX, bool CHECK_TAIL, bool FILTER = false>
 __device__ __forceinline__ void compute_step(const FwdParams &p, uint32_t ksm, uint32_t vsm, const uint32_t *bm32,
                                              int n_valid, int t8_first, const uint32_t (&qa)[D / 16][4],
                                              float (&o)[D / 8][4], float (&m_run)[2], float (&l_run)[2], int lane,
-                                             int bm_shift) {
+                                             int bm_shift, uint32_t cm = 0xffffffffu) {
   float s[NT8][4];
   score_tiles<D, NT8>(ksm, qa, s, lane);
-  softmax_pv<D, NT8, SOFTMAX, CHECK_TAIL>(p, s, vsm, bm32, n_valid, t8_first, o, m_run, l_run, lane, bm_shift);
+  softmax_pv<D, NT8, SOFTMAX, CHECK_TAIL, true, FILTER>(p, s, vsm, bm32, n_valid, t8_first, o, m_run, l_run, lane,
+                                                       bm_shift, cm);
 }
 
-template <int D, int NT8, bool SOFTMAX, bool CHECK_TAIL, bool SDDMM>
+template <int D, int NT8, bool SOFTMAX, bool CHECK_TAIL, bool SDDMM, bool FILTER>
 __device__ __forceinline__ void softmax_pv(const FwdParams &p, float (&s)[NT8][4], uint32_t vsm, const uint32_t *bm32,
                                            int n_valid, int t8_first, float (&o)[D / 8][4], float (&m_run)[2],
-                                           float (&l_run)[2], int lane, int bm_shift) {
+                                           float (&l_run)[2], int lane, int bm_shift, uint32_t cm) {
   using T = Tile<D>;
   constexpr int NF = D / 8;
   const int g = lane >> 2, qd = lane & 3;
@@ -73,6 +75,12 @@ __device__ __forceinline__ void softmax_pv(const FwdParams &p, float (&s)[NT8][4
   for (int nt = 0; nt < NT8; ++nt) {
     uint32_t h0 = bm32[nt * 4] << bm_shift, h1 = bm32[nt * 4 + 2] << bm_shift;
     if (CHECK_TAIL && nt >= n_valid) h0 = h1 = 0u;
+    if (FILTER) {  // columns 2qd and 2qd+1 of tile nt: clear their occupancy bits unless the column takes part
+      const uint32_t cb = cm >> (nt * 8 + 2 * qd);
+      const uint32_t keep = ((cb & 1u) << 31) | ((cb & 2u) << 29);
+      h0 &= keep;
+      h1 &= keep;
+    }
     const bool v0 = (int)h0 < 0, v1 = (int)(h0 << 1) < 0, v2 = (int)h1 < 0, v3 = (int)(h1 << 1) < 0;
     if (SDDMM && p.sddmm != nullptr) {
       if (nt < n_valid) {
@@ -215,6 +223,31 @@ __device__ __forceinline__ void store_output(const FwdParams &p, int head, int w
     store_tile<D>(p, head, window, f, o[f][0] * inv0, o[f][1] * inv0, o[f][2] * inv1, o[f][3] * inv1, lane);
 }
 
+// Two-phase calls: the unnormalised result of a window (running max, running sum, accumulator) is
+// carried from the first launch to the second through state[], in the layout of a partial.
+template <int D>
+__device__ __forceinline__ float *state_slot(const FwdParams &p, int head, int window) {
+  constexpr int PARTIAL_FLOATS = ((D / 8) * 4 + 4) * 32;
+  return p.state + ((size_t)head * p.n_rw + window) * PARTIAL_FLOATS;
+}
+
+// Start of a unit of the second launch: the first chunk of a window continues from the carried state.
+template <int D>
+__device__ __forceinline__ void load_state(const FwdParams &p, const Unit &u, float (&o)[D / 8][4],
+                                           float (&m_run)[2], float (&l_run)[2], int lane) {
+  constexpr int NF = D / 8;
+  if (p.phase != 2 || u.chunk != 0) return;
+  const float *st = state_slot<D>(p, u.head, u.window);
+#pragma unroll
+  for (int f = 0; f < NF; ++f)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[f][e] = __ldcg(st + (f * 4 + e) * 32 + lane);
+  m_run[0] = __ldcg(st + (NF * 4 + 0) * 32 + lane);
+  m_run[1] = __ldcg(st + (NF * 4 + 1) * 32 + lane);
+  l_run[0] = __ldcg(st + (NF * 4 + 2) * 32 + lane);
+  l_run[1] = __ldcg(st + (NF * 4 + 3) * 32 + lane);
+}
+
 // End of a unit: reduce the row sums, publish / merge partials of a split window, store.
 template <int D, bool SOFTMAX>
 __device__ __forceinline__ void finish_unit(const FwdParams &p, const Unit &u, float (&o)[D / 8][4],
@@ -248,10 +281,10 @@ __device__ __forceinline__ void finish_unit(const FwdParams &p, const Unit &u, f
           mm[0] = fmaxf(mm[0], __ldcg(pc + (NF * 4 + 0) * 32 + lane));
           mm[1] = fmaxf(mm[1], __ldcg(pc + (NF * 4 + 1) * 32 + lane));
         }
+        m_run[0] = mm[0];  // may be -inf (no column seen yet): what a carried state must say
+        m_run[1] = mm[1];
         if (mm[0] == NEG_INF) mm[0] = 0.f;
         if (mm[1] == NEG_INF) mm[1] = 0.f;
-        m_run[0] = mm[0];
-        m_run[1] = mm[1];
       }
 #pragma unroll
       for (int f = 0; f < NF; ++f) o[f][0] = o[f][1] = o[f][2] = o[f][3] = 0.f;
@@ -273,9 +306,24 @@ __device__ __forceinline__ void finish_unit(const FwdParams &p, const Unit &u, f
           o[f][3] += w1 * __ldcg(pc + (f * 4 + 3) * 32 + lane);
         }
       }
+      // every chunk has arrived and been read: leave the counter at zero for the next launch
+      if (lane == 0) p.arrive[(size_t)u.head * p.max_slots + u.slot_base] = 0;
     }
   }
-  if (write_out) store_output<D, SOFTMAX>(p, u.head, u.window, o, m_run, l_run, lane);
+  if (!write_out) return;
+  if (p.phase == 1) {  // first launch of a two-phase call: carry the unnormalised result
+    float *st = state_slot<D>(p, u.head, u.window);
+#pragma unroll
+    for (int f = 0; f < NF; ++f)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) __stcg(st + (f * 4 + e) * 32 + lane, o[f][e]);
+    __stcg(st + (NF * 4 + 0) * 32 + lane, m_run[0]);
+    __stcg(st + (NF * 4 + 1) * 32 + lane, m_run[1]);
+    __stcg(st + (NF * 4 + 2) * 32 + lane, l_run[0]);
+    __stcg(st + (NF * 4 + 3) * 32 + lane, l_run[1]);
+    return;
+  }
+  store_output<D, SOFTMAX>(p, u.head, u.window, o, m_run, l_run, lane);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -290,7 +338,7 @@ struct FwdCfg {
   static constexpr int Q_BYTES = 16 * D * 2;
   static constexpr int WARP_BYTES = Q_BYTES + STAGES * STAGE_BYTES;
   static constexpr int SMEM_BYTES = WARPS * WARP_BYTES;
-  static_assert(NT8 * 16 <= BM_BYTES, "bitmap slot too small");
+  static_assert(NT8 * 16 + 4 <= BM_BYTES, "bitmap slot too small (bitmap words + one column-mask word)");
   static_assert(NT8 % 2 == 0 && ROWS <= 32, "a step is 16 or 32 gathered columns");
   static_assert(SMEM_BYTES + WARPS * UNIT_DESC_INTS * 4 <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
@@ -314,7 +362,7 @@ struct WarpStage {
 
 // The fused loop of one unit (window `window` of head `head`, tiles [t8b, t8e)) on the combined-stage
 // cp.async path; accumulates into o / m_run / l_run.  All copies have landed when it returns.
-template <int D, int NT8, int STAGES, int WARPS, bool SOFTMAX>
+template <int D, int NT8, int STAGES, int WARPS, bool SOFTMAX, bool FILTER = false>
 __device__ __forceinline__ void run_unit_cpasync(const FwdParams &p, const WarpStage<D, NT8, STAGES, WARPS> &ws,
                                                  int head, int window, int t8b, int t8e, float (&o)[D / 8][4],
                                                  float (&m_run)[2], float (&l_run)[2], int lane) {
@@ -350,7 +398,15 @@ __device__ __forceinline__ void run_unit_cpasync(const FwdParams &p, const WarpS
     const uint32_t vs = ks + C::TILE_BYTES;
     const uint32_t bs = vs + C::TILE_BYTES;
     const int lim = (t8e - t8) * 8;  // rows at or beyond lim lie outside the unit
-    const int idx_cur = idx_next;
+    int idx_cur = idx_next;
+    if (FILTER) {  // which of the step's columns take part in this launch; kept beside the bitmap words
+      const bool take = p.phase == 1 ? idx_cur >= p.col_split : idx_cur < p.col_split;
+      const uint32_t cm = __ballot_sync(FULL, take);
+      if (lane == 0) asm volatile("st.shared.u32 [%0], %1;" ::"r"(bs + NT8 * 16), "r"(cm) : "memory");
+      // The first launch runs before the other ranks' rows have arrived: a column that does not take part
+      // must not even be read there (0 x stale NaN would poison the accumulator), so it reads an own row.
+      if (p.phase == 1 && !take) idx_cur = p.col_split;
+    }
     {
       const int t8n = t8 + NT8;
       const int limn = (t8e - t8n) * 8;
@@ -364,7 +420,7 @@ __device__ __forceinline__ void run_unit_cpasync(const FwdParams &p, const WarpS
       const int idx = __shfl_sync(FULL, idx_cur, r);
       const bool real = ch * 8 < p.d_real;
       const int nbytes = (r < lim && real) ? 16 : 0;
-      const size_t off = (size_t)idx * p.ld + (real ? ch * 8 : 0);
+      const size_t off = (size_t)idx * p.ld_kv + (real ? ch * 8 : 0);
       cp_async16(T::addr(ks, r, ch), kb + off, nbytes);
       cp_async16(T::addr(vs, r, ch), vb + off, nbytes);
     }
@@ -391,14 +447,17 @@ __device__ __forceinline__ void run_unit_cpasync(const FwdParams &p, const WarpS
     const uint32_t *bm32 =
         reinterpret_cast<const uint32_t *>(ws.stage0_g + st * C::STAGE_BYTES + 2 * C::TILE_BYTES) + ws.bm_half;
     const int t8 = t8b + step * NT8;
-    compute_step<D, NT8, SOFTMAX, false>(p, ksm, vsm, bm32, min(NT8, t8e - t8), t8, qa, o, m_run, l_run, lane,
-                                         ws.bm_shift);
+    uint32_t cm = 0xffffffffu;
+    if (FILTER)
+      cm = *reinterpret_cast<const uint32_t *>(ws.stage0_g + st * C::STAGE_BYTES + 2 * C::TILE_BYTES + NT8 * 16);
+    compute_step<D, NT8, SOFTMAX, false, FILTER>(p, ksm, vsm, bm32, min(NT8, t8e - t8), t8, qa, o, m_run, l_run, lane,
+                                                 ws.bm_shift, cm);
     __syncwarp();  // every lane is done with this stage before it is refilled
   }
   cp_async_wait<0>();
 }
 
-template <int D, int NT8, int STAGES, int WARPS, bool SOFTMAX>
+template <int D, int NT8, int STAGES, int WARPS, bool SOFTMAX, bool FILTER = false>
 __global__ void __launch_bounds__(WARPS * 32, 1) fwd_kernel(const FwdParams p) {
   using C = FwdCfg<D, NT8, STAGES, WARPS>;
   constexpr int NF = D / 8;
@@ -418,9 +477,12 @@ __global__ void __launch_bounds__(WARPS * 32, 1) fwd_kernel(const FwdParams p) {
     for (int f = 0; f < NF; ++f) o[f][0] = o[f][1] = o[f][2] = o[f][3] = 0.f;
     float m_run[2] = {NEG_INF, NEG_INF};  // running max of the raw (unscaled) scores, rows g and g+8
     float l_run[2] = {0.f, 0.f};          // running sum of rows g and g+8
-    run_unit_cpasync<D, NT8, STAGES, WARPS, SOFTMAX>(p, ws, u.head, u.window, u.t8b, u.t8e, o, m_run, l_run, lane);
+    if (FILTER) load_state<D>(p, u, o, m_run, l_run, lane);
+    run_unit_cpasync<D, NT8, STAGES, WARPS, SOFTMAX, FILTER>(p, ws, u.head, u.window, u.t8b, u.t8e, o, m_run, l_run,
+                                                             lane);
     finish_unit<D, SOFTMAX>(p, u, o, m_run, l_run, lane);
   }
+  retire_warp(p, lane, gridDim.x * WARPS);
   trace_end(p, lane);
 }
 
@@ -584,7 +646,7 @@ struct SplitCfg {
   static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 };
 
-template <int WARPS, bool SOFTMAX>
+template <int WARPS, bool SOFTMAX, bool FILTER = false>
 __global__ void __launch_bounds__(WARPS * 32, 1) fwd_kernel_split(const FwdParams p) {
   using C = SplitCfg<WARPS>;
   constexpr int D = C::D, NT8 = C::NT8, TILE = C::TILE_BYTES;
@@ -607,7 +669,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) fwd_kernel_split(const FwdParam
   const int rl = lane >> 3, ch = lane & 7;
   const uint32_t off_even = rl * 128 + ((ch ^ rl) << 4);
   const uint32_t off_odd = rl * 128 + ((ch ^ (rl | 4)) << 4);
-  const unsigned ld_bytes = (unsigned)(p.ld * 2);
+  const unsigned ld_bytes = (unsigned)(p.ld_kv * 2);
 
   trace_begin(p);
   UnitSource src;
@@ -623,6 +685,9 @@ __global__ void __launch_bounds__(WARPS * 32, 1) fwd_kernel_split(const FwdParam
     for (int f = 0; f < NF; ++f) o[f][0] = o[f][1] = o[f][2] = o[f][3] = 0.f;
     float m_run[2] = {NEG_INF, NEG_INF};
     float l_run[2] = {0.f, 0.f};
+    if (FILTER) load_state<D>(p, u, o, m_run, l_run, lane);
+    // FILTER: which columns of the step being computed / the next / the one after take part
+    uint32_t cm_cur = 0xffffffffu, cm_n1 = 0xffffffffu, cm_n2 = 0xffffffffu;
 
     if (nsteps > 0) {
       {  // Q window -> shared (first copy group); rows past the last node read as 0
@@ -646,6 +711,13 @@ __global__ void __launch_bounds__(WARPS * 32, 1) fwd_kernel_split(const FwdParam
       auto issue_k = [&](int step) {
         const uint32_t dst = k_s + (step & 1) * TILE;
         idx_kv = idx_next;
+        if (FILTER) {
+          const bool take = p.phase == 1 ? idx_kv >= p.col_split : idx_kv < p.col_split;
+          cm_n2 = __ballot_sync(FULL, take);
+          // first launch: columns that do not take part may not have arrived yet and are not read at all
+          // (0 x stale NaN would poison the accumulator); they read an own row instead
+          if (p.phase == 1 && !take) idx_kv = p.col_split;
+        }
         {
           const int t8n = t8b + (step + 1) * NT8;
           const int limn = (t8e - t8n) * 8;
@@ -673,10 +745,12 @@ __global__ void __launch_bounds__(WARPS * 32, 1) fwd_kernel_split(const FwdParam
       };
       issue_k(0);
       cp_async_commit();
+      cm_cur = cm_n2;
       issue_v(0);
       cp_async_commit();
       if (nsteps > 1) issue_k(1);
       cp_async_commit();
+      cm_n1 = cm_n2;
       cp_async_wait<2>();  // Q and K of step 0 have landed
       __syncwarp();
       uint32_t qa[KS][4];
@@ -695,8 +769,11 @@ __global__ void __launch_bounds__(WARPS * 32, 1) fwd_kernel_split(const FwdParam
         if (step + 1 < nsteps) score_tiles<D, NT8>(k_s + ((step + 1) & 1) * TILE, qa, s_next, lane);
         const uint32_t *bm32 = reinterpret_cast<const uint32_t *>(bm_g + (step & 1) * 128) + bm_half;
         const int t8 = t8b + step * NT8;
-        softmax_pv<D, NT8, SOFTMAX, false, false>(p, s_cur, v_s + (step & 1) * TILE, bm32, min(NT8, t8e - t8), t8, o,
-                                                  m_run, l_run, lane, bm_shift);
+        softmax_pv<D, NT8, SOFTMAX, false, false, FILTER>(p, s_cur, v_s + (step & 1) * TILE, bm32,
+                                                          min(NT8, t8e - t8), t8, o, m_run, l_run, lane, bm_shift,
+                                                          cm_cur);
+        cm_cur = cm_n1;
+        cm_n1 = cm_n2;
         __syncwarp();  // this step's K, V and bitmap buffers may be refilled
 #pragma unroll
         for (int nt = 0; nt < NT8; ++nt)
@@ -707,6 +784,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) fwd_kernel_split(const FwdParam
     }
     finish_unit<D, SOFTMAX>(p, u, o, m_run, l_run, lane);
   }
+  retire_warp(p, lane, gridDim.x * WARPS);
   trace_end(p, lane);
 }
 
@@ -878,6 +956,7 @@ fwd_kernel_tma(const FwdParams p, const __grid_constant__ CUtensorMap tmq, const
     }
     finish_unit<D, SOFTMAX>(p, u, o, m_run, l_run, lane);
   }
+  retire_warp(p, lane, gridDim.x * WARPS);
   trace_end(p, lane);
 }
 
@@ -943,15 +1022,19 @@ static void layout(Geometry &gm, long long total_t8, int heads, int d) {
 }
 
 // budget_bytes > 0: raise the split threshold (fewer, larger chunks) until the scratch fits.
-static Geometry geometry(int n_rw, long long n_tcb, int block_w, int heads, int d, size_t budget_bytes = 0) {
+// phased: geometry of one launch of a two-phase call -- always scheduled (never the one-launch mode), never
+// the TMA path, and room in the unit list for the TC block per window that both launches work on.
+static Geometry geometry(int n_rw, long long n_tcb, int block_w, int heads, int d, size_t budget_bytes = 0,
+                         bool phased = false) {
   Geometry gm;
   const int d_real = d;
   d = padded_dim(d);
   gm.kc = kernel_cfg(d);
   if (d_real != d) gm.kc.path = PATH_CPASYNC;  // only the plain kernel zero-fills padded chunks
-  const long long total_t8 = n_tcb * (block_w / 8);
+  if (phased && gm.kc.path == PATH_TMA) gm.kc.path = PATH_SPLIT;
+  const long long total_t8 = (n_tcb + (phased ? n_rw : 0)) * (block_w / 8);
   const long long total_warps = (long long)sm_count() * gm.kc.warps;
-  gm.direct = (total_t8 * heads <= total_warps * DIRECT_TILES_PER_WARP) ? 1 : 0;
+  gm.direct = (!phased && total_t8 * heads <= total_warps * DIRECT_TILES_PER_WARP) ? 1 : 0;
   // Many short windows (fewer than four 32-column steps on average, e.g. batches of small graphs):
   // the split-ring kernel's longer prologue costs more than its overlap gains (measured 0.31 vs
   // 0.21 ms on the molecule-batch workload), so the plain two-stage kernel is used there.
@@ -974,6 +1057,18 @@ static Geometry geometry(int n_rw, long long n_tcb, int block_w, int heads, int 
 template <int D, int NT8, int STAGES, int WARPS>
 static int launch(const FwdParams &p, bool softmax, int grid, cudaStream_t stream) {
   using C = FwdCfg<D, NT8, STAGES, WARPS>;
+  if (p.phase != 0) {  // two-phase calls exist with softmax only
+    if constexpr (D == 64) {
+      auto kern = fwd_kernel<D, NT8, STAGES, WARPS, true, true>;
+      F3S_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+      kern<<<grid, WARPS * 32, C::SMEM_BYTES, stream>>>(p);
+      F3S_CHECK_LAUNCH();
+      return F3S_OK;
+    } else {
+      set_error("two-phase calls need head_dim 64");
+      return F3S_ERR_UNSUPPORTED;
+    }
+  }
   if (softmax) {
     auto kern = fwd_kernel<D, NT8, STAGES, WARPS, true>;
     F3S_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
@@ -1042,8 +1137,8 @@ static int launch_tma(const FwdParams &p, bool softmax, int grid, cudaStream_t s
   // Q: exact row count, so that rows past the last node are zero-filled by the hardware.
   if (int rc = make_map(&tmq, p.q, p.ld, (unsigned long long)p.n_nodes, 64, 16)) return rc;
   // K, V: the row count is not an argument of the C ABI; every column id must have a row.
-  if (int rc = make_map(&tmk, p.k, p.ld, 1ull << 31, 64, 1)) return rc;
-  if (int rc = make_map(&tmv, p.v, p.ld, 1ull << 31, 64, 1)) return rc;
+  if (int rc = make_map(&tmk, p.k, p.ld_kv, 1ull << 31, 64, 1)) return rc;
+  if (int rc = make_map(&tmv, p.v, p.ld_kv, 1ull << 31, 64, 1)) return rc;
   const int smem = tma::smem_bytes(WARPS);
   if (softmax) {
     auto kern = fwd_kernel_tma<WARPS, true>;
@@ -1061,6 +1156,13 @@ static int launch_tma(const FwdParams &p, bool softmax, int grid, cudaStream_t s
 template <int WARPS>
 static int launch_split(const FwdParams &p, bool softmax, int grid, cudaStream_t stream) {
   using C = SplitCfg<WARPS>;
+  if (p.phase != 0) {  // two-phase calls exist with softmax only
+    auto kern = fwd_kernel_split<WARPS, true, true>;
+    F3S_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+    kern<<<grid, WARPS * 32, C::SMEM_BYTES, stream>>>(p);
+    F3S_CHECK_LAUNCH();
+    return F3S_OK;
+  }
   if (softmax) {
     auto kern = fwd_kernel_split<WARPS, true>;
     F3S_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
@@ -1090,6 +1192,16 @@ extern "C" size_t f3s_forward_workspace_bytes(int32_t n_row_windows, int64_t n_t
 static int g_unit_list_limit = 0;
 extern "C" void f3s_debug_set_unit_list_limit(int32_t limit) { g_unit_list_limit = limit > 0 ? limit : 0; }
 
+// Options of the entry points that go beyond f3s_forward.
+struct FwdExtra {
+  int64_t ld_kv = 0;                  // row stride of k and v (0: same as q's)
+  int mode = 0;                       // 0: schedule + launch; 1: schedule only; 2: launch on a scratch scheduled before
+  int phase = 0, col_split = 0;       // see FwdParams
+  const int32_t *phase_split = nullptr;
+  float *state = nullptr;
+};
+enum { MODE_FULL = 0, MODE_PLAN_ONLY = 1, MODE_PLANNED = 2 };
+
 // Validation + launch shared by the entry points.  budget_bytes > 0 lets the schedule use
 // fewer, larger chunks so that its scratch fits in that many bytes.
 static int forward_impl(const int32_t *row_window_offset, const int32_t *sorted_row_windows,
@@ -1098,8 +1210,11 @@ static int forward_impl(const int32_t *row_window_offset, const int32_t *sorted_
                         int64_t ld, const void *q, const void *k, const void *v, float scale_divisor,
                         int32_t apply_softmax, void *out, int out_is_half, float *sddmm_out, void *workspace,
                         size_t workspace_bytes, size_t budget_bytes, uint64_t *sm_trace, float *lse,
-                        f3s_stream_t stream_) {
+                        f3s_stream_t stream_, const FwdExtra *extra = nullptr) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const FwdExtra ex = extra ? *extra : FwdExtra{};
+  const int64_t ld_kv = ex.ld_kv > 0 ? ex.ld_kv : ld;
+  const bool plan_only = ex.mode == MODE_PLAN_ONLY;
   F3S_REQUIRE(num_nodes >= 0 && n_row_windows >= 0 && n_tcb >= 0, F3S_ERR_INVALID_ARG, "negative size");
   F3S_REQUIRE(n_row_windows == (num_nodes + 15) / 16, F3S_ERR_INVALID_ARG,
               "n_row_windows (%d) must be ceil(num_nodes/16) (%d)", n_row_windows, (num_nodes + 15) / 16);
@@ -1107,19 +1222,27 @@ static int forward_impl(const int32_t *row_window_offset, const int32_t *sorted_
   F3S_REQUIRE(dim_supported(head_dim), F3S_ERR_UNSUPPORTED,
               "head_dim must be a multiple of 16 between 16 and 128, got %d", head_dim);
   F3S_REQUIRE(heads >= 1, F3S_ERR_INVALID_ARG, "heads must be >= 1");
-  F3S_REQUIRE(ld >= (int64_t)heads * head_dim && ld % 8 == 0, F3S_ERR_INVALID_ARG,
-              "ld (%lld) must be >= heads*head_dim and a multiple of 8", (long long)ld);
-  F3S_REQUIRE(scale_divisor != 0.f && isfinite(scale_divisor), F3S_ERR_INVALID_ARG,
+  F3S_REQUIRE(plan_only || (ld >= (int64_t)heads * head_dim && ld % 8 == 0 && ld_kv >= (int64_t)heads * head_dim &&
+                            ld_kv % 8 == 0),
+              F3S_ERR_INVALID_ARG, "row strides (%lld, %lld) must be >= heads*head_dim and multiples of 8",
+              (long long)ld, (long long)ld_kv);
+  F3S_REQUIRE(plan_only || (scale_divisor != 0.f && isfinite(scale_divisor)), F3S_ERR_INVALID_ARG,
               "scale_divisor must be finite and non-zero");
   F3S_REQUIRE(n_tcb * block_w < (1ll << 31), F3S_ERR_UNSUPPORTED, "n_tcb*block_w exceeds int32");
+  F3S_REQUIRE(ex.phase >= 0 && ex.phase <= 2, F3S_ERR_INVALID_ARG, "phase must be 0, 1 or 2");
+  F3S_REQUIRE(ex.phase == 0 || (head_dim == 64 && apply_softmax && ex.phase_split && (plan_only || ex.state)),
+              F3S_ERR_UNSUPPORTED, "two-phase calls need head_dim 64, softmax, phase_split and a state array");
   if (num_nodes == 0) return F3S_OK;
-  F3S_REQUIRE(row_window_offset && q && k && v && out, F3S_ERR_INVALID_ARG, "null pointer argument");
-  F3S_REQUIRE(n_tcb == 0 || (sparse_a_to_x_idx && tcb_bitmap), F3S_ERR_INVALID_ARG, "null TCB array");
-  F3S_REQUIRE(sddmm_out == nullptr || heads == 1, F3S_ERR_INVALID_ARG, "sddmm_out needs heads == 1");
+  F3S_REQUIRE(row_window_offset, F3S_ERR_INVALID_ARG, "null pointer argument");
   auto misaligned = [](const void *ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) != 0; };
-  F3S_REQUIRE(!misaligned(q) && !misaligned(k) && !misaligned(v) && !misaligned(out) && !misaligned(tcb_bitmap),
-              F3S_ERR_INVALID_ARG, "q, k, v, out and tcb_bitmap must be 16-byte aligned");
-  Geometry gm = geometry(n_row_windows, n_tcb, block_w, heads, head_dim, budget_bytes);
+  if (!plan_only) {
+    F3S_REQUIRE(q && k && v && (out || ex.phase == 1), F3S_ERR_INVALID_ARG, "null pointer argument");
+    F3S_REQUIRE(n_tcb == 0 || (sparse_a_to_x_idx && tcb_bitmap), F3S_ERR_INVALID_ARG, "null TCB array");
+    F3S_REQUIRE(sddmm_out == nullptr || heads == 1, F3S_ERR_INVALID_ARG, "sddmm_out needs heads == 1");
+    F3S_REQUIRE(!misaligned(q) && !misaligned(k) && !misaligned(v) && !misaligned(out) && !misaligned(tcb_bitmap),
+                F3S_ERR_INVALID_ARG, "q, k, v, out and tcb_bitmap must be 16-byte aligned");
+  }
+  Geometry gm = geometry(n_row_windows, n_tcb, block_w, heads, head_dim, budget_bytes, ex.phase != 0);
   if (!gm.direct && g_unit_list_limit > 0 && gm.max_slots > g_unit_list_limit) gm.max_slots = g_unit_list_limit;
   F3S_REQUIRE(workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255) == 0, F3S_ERR_WORKSPACE,
               "workspace must be non-null and 256-byte aligned");
@@ -1144,6 +1267,11 @@ static int forward_impl(const int32_t *row_window_offset, const int32_t *sorted_
   p.heads = heads;
   p.d_real = head_dim;
   p.ld = ld;
+  p.ld_kv = ld_kv;
+  p.phase = ex.phase;
+  p.col_split = ex.col_split;
+  p.phase_split = ex.phase_split;
+  p.state = ex.state;
   p.t8_per_tcb = block_w / 8;
   p.direct = gm.direct;
   p.ch8 = gm.direct ? INT_MAX : gm.ch8;
@@ -1161,13 +1289,14 @@ static int forward_impl(const int32_t *row_window_offset, const int32_t *sorted_
   if (gm.direct) {  // one launch; no more CTAs than there are (head, window) pairs
     const long long units = (long long)n_row_windows * heads;
     if (units < grid) grid = (int)(units > 0 ? units : 1);
-  } else {
+  } else if (ex.mode != MODE_PLANNED) {
     F3S_CUDA_TRY(cudaMemsetAsync(ws + gm.off_hdr, 0, gm.zero_bytes, stream));
     plan_kernel<<<(n_row_windows + PLAN_THREADS - 1) / PLAN_THREADS, PLAN_THREADS, 0, stream>>>(
-        row_window_offset, sorted_row_windows, n_row_windows, p.t8_per_tcb, gm.ch8, gm.kc.nt8, p.hdr,
-        reinterpret_cast<UnitDesc *>(ws + gm.off_units), gm.max_slots);
+        PlanArgs{row_window_offset, ex.phase, ex.phase_split}, sorted_row_windows, n_row_windows, p.t8_per_tcb,
+        gm.ch8, gm.kc.nt8, p.hdr, reinterpret_cast<UnitDesc *>(ws + gm.off_units), gm.max_slots);
     F3S_CHECK_LAUNCH();
   }
+  if (plan_only) return F3S_OK;
   const bool sm = apply_softmax != 0;
   const KernelCfg kc = gm.kc;
   if (gm.direct) {
@@ -1241,6 +1370,110 @@ extern "C" int f3s_forward_traced(const int32_t *row_window_offset, const int32_
   return forward_impl(row_window_offset, sorted_row_windows, sparse_a_to_x_idx, tcb_bitmap, num_nodes, n_row_windows,
                       n_tcb, block_w, heads, head_dim, ld, q, k, v, scale_divisor, apply_softmax, out, 0, nullptr,
                       workspace, workspace_bytes, 0, sm_trace, nullptr, stream);
+}
+
+// ---------------------------------------------------------------------------------------
+// Repeated calls on one graph: schedule once, then one kernel launch per call.
+// ---------------------------------------------------------------------------------------
+extern "C" int f3s_forward_plan(const int32_t *row_window_offset, const int32_t *sorted_row_windows,
+                                int32_t num_nodes, int32_t n_row_windows, int64_t n_tcb, int32_t block_w,
+                                int32_t heads, int32_t head_dim, void *workspace, size_t workspace_bytes,
+                                f3s_stream_t stream) {
+  FwdExtra ex;
+  ex.mode = MODE_PLAN_ONLY;
+  return forward_impl(row_window_offset, sorted_row_windows, nullptr, nullptr, num_nodes, n_row_windows, n_tcb,
+                      block_w, heads, head_dim, 0, nullptr, nullptr, nullptr, 1.f, 1, nullptr, 0, nullptr, workspace,
+                      workspace_bytes, 0, nullptr, nullptr, stream, &ex);
+}
+
+extern "C" int f3s_forward_planned(const int32_t *row_window_offset, const int32_t *sorted_row_windows,
+                                   const int32_t *sparse_a_to_x_idx, const uint64_t *tcb_bitmap, int32_t num_nodes,
+                                   int32_t n_row_windows, int64_t n_tcb, int32_t block_w, int32_t heads,
+                                   int32_t head_dim, int64_t ld_q, const void *q, int64_t ld_kv, const void *k,
+                                   const void *v, float scale_divisor, int32_t apply_softmax, void *out,
+                                   int32_t out_is_half, void *workspace, size_t workspace_bytes,
+                                   f3s_stream_t stream) {
+  FwdExtra ex;
+  ex.mode = MODE_PLANNED;
+  ex.ld_kv = ld_kv;
+  return forward_impl(row_window_offset, sorted_row_windows, sparse_a_to_x_idx, tcb_bitmap, num_nodes, n_row_windows,
+                      n_tcb, block_w, heads, head_dim, ld_q, q, k, v, scale_divisor, apply_softmax, out,
+                      out_is_half ? 1 : 0, nullptr, workspace, workspace_bytes, 0, nullptr, nullptr, stream, &ex);
+}
+
+// ---------------------------------------------------------------------------------------
+// Two-phase calls: first the columns a rank already holds, then -- once they have arrived -- the rest.
+// Scratch: [schedule of phase 1][schedule of phase 2][state of every (head, window)].
+// ---------------------------------------------------------------------------------------
+namespace {
+struct PhasedLayout {
+  size_t sched_bytes, off_state, total;
+};
+PhasedLayout phased_layout(int n_rw, long long n_tcb, int block_w, int heads, int d) {
+  PhasedLayout L;
+  L.sched_bytes = align_up(geometry(n_rw, n_tcb, block_w, heads, d, 0, true).total_bytes, 256);
+  L.off_state = 2 * L.sched_bytes;
+  const size_t partial_floats = (size_t)((padded_dim(d) / 8) * 4 + 4) * 32;
+  L.total = L.off_state + align_up((size_t)n_rw * heads * partial_floats * sizeof(float), 256);
+  return L;
+}
+}  // namespace
+
+extern "C" size_t f3s_forward_phased_workspace_bytes(int32_t n_row_windows, int64_t n_tcb, int32_t block_w,
+                                                     int32_t heads, int32_t head_dim) {
+  if (n_row_windows < 0 || n_tcb < 0 || heads < 1 || (block_w != 8 && block_w != 16) || head_dim != 64) return 0;
+  return phased_layout(n_row_windows, n_tcb, block_w, heads, head_dim).total;
+}
+
+extern "C" int f3s_forward_phased_plan(const int32_t *row_window_offset, const int32_t *sorted_row_windows,
+                                       const int32_t *phase_split, int32_t num_nodes, int32_t n_row_windows,
+                                       int64_t n_tcb, int32_t block_w, int32_t heads, int32_t head_dim,
+                                       void *workspace, size_t workspace_bytes, f3s_stream_t stream) {
+  F3S_REQUIRE(head_dim == 64, F3S_ERR_UNSUPPORTED, "two-phase calls need head_dim 64");
+  F3S_REQUIRE(n_row_windows >= 0 && n_tcb >= 0 && heads >= 1 && (block_w == 8 || block_w == 16), F3S_ERR_INVALID_ARG,
+              "bad size");
+  const PhasedLayout L = phased_layout(n_row_windows, n_tcb, block_w, heads, head_dim);
+  F3S_REQUIRE(workspace && workspace_bytes >= L.total, F3S_ERR_WORKSPACE, "workspace too small: %zu < %zu",
+              workspace_bytes, L.total);
+  unsigned char *ws = static_cast<unsigned char *>(workspace);
+  for (int phase = 1; phase <= 2; ++phase) {
+    FwdExtra ex;
+    ex.mode = MODE_PLAN_ONLY;
+    ex.phase = phase;
+    ex.phase_split = phase_split;
+    if (int rc = forward_impl(row_window_offset, sorted_row_windows, nullptr, nullptr, num_nodes, n_row_windows, n_tcb,
+                              block_w, heads, head_dim, 0, nullptr, nullptr, nullptr, 1.f, 1, nullptr, 0, nullptr,
+                              ws + (phase - 1) * L.sched_bytes, L.sched_bytes, 0, nullptr, nullptr, stream, &ex))
+      return rc;
+  }
+  return F3S_OK;
+}
+
+extern "C" int f3s_forward_phase(int32_t phase, const int32_t *row_window_offset, const int32_t *sorted_row_windows,
+                                 const int32_t *sparse_a_to_x_idx, const uint64_t *tcb_bitmap,
+                                 const int32_t *phase_split, int32_t col_split, int32_t num_nodes,
+                                 int32_t n_row_windows, int64_t n_tcb, int32_t block_w, int32_t heads,
+                                 int32_t head_dim, int64_t ld_q, const void *q, int64_t ld_kv, const void *k,
+                                 const void *v, float scale_divisor, float *out, void *workspace,
+                                 size_t workspace_bytes, f3s_stream_t stream) {
+  F3S_REQUIRE(phase == 1 || phase == 2, F3S_ERR_INVALID_ARG, "phase must be 1 or 2");
+  F3S_REQUIRE(head_dim == 64, F3S_ERR_UNSUPPORTED, "two-phase calls need head_dim 64");
+  F3S_REQUIRE(n_row_windows >= 0 && n_tcb >= 0 && heads >= 1 && (block_w == 8 || block_w == 16), F3S_ERR_INVALID_ARG,
+              "bad size");
+  const PhasedLayout L = phased_layout(n_row_windows, n_tcb, block_w, heads, head_dim);
+  F3S_REQUIRE(workspace && workspace_bytes >= L.total, F3S_ERR_WORKSPACE, "workspace too small: %zu < %zu",
+              workspace_bytes, L.total);
+  unsigned char *ws = static_cast<unsigned char *>(workspace);
+  FwdExtra ex;
+  ex.mode = MODE_PLANNED;
+  ex.ld_kv = ld_kv;
+  ex.phase = phase;
+  ex.col_split = col_split;
+  ex.phase_split = phase_split;
+  ex.state = reinterpret_cast<float *>(ws + L.off_state);
+  return forward_impl(row_window_offset, sorted_row_windows, sparse_a_to_x_idx, tcb_bitmap, num_nodes, n_row_windows,
+                      n_tcb, block_w, heads, head_dim, ld_q, q, k, v, scale_divisor, 1, out, 0, nullptr,
+                      ws + (phase - 1) * L.sched_bytes, L.sched_bytes, 0, nullptr, nullptr, stream, &ex);
 }
 
 // Reads the status word the kernels of the last forward call on `workspace` left behind.

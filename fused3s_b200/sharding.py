@@ -37,12 +37,21 @@ import numpy as np
 from . import cabi
 
 
-def partition_rows(rowptr: np.ndarray, num_nodes: int, n_parts: int) -> np.ndarray:
-    """Row cut points (multiples of 16, last = num_nodes) of a contiguous partition of the
-    row windows with near-equal edge counts.  Returns int64[n_parts + 1]."""
+def partition_rows(rowptr: np.ndarray, num_nodes: int, n_parts: int, window_weight: np.ndarray | None = None) -> np.ndarray:
+    """Row cut points (multiples of 16, last = num_nodes) of a contiguous partition of the row windows
+    with near-equal total weight.  ``window_weight[w]`` is the cost of window w -- its TC-block count is
+    what the fused kernel's time follows (``cabi.window_tcb_counts``); without it the edge count from
+    ``rowptr`` stands in.  Returns int64[n_parts + 1]."""
     n_rw = (num_nodes + 15) // 16
-    win_rows = np.minimum(np.arange(n_rw + 1, dtype=np.int64) * 16, num_nodes)
-    prefix = np.ascontiguousarray(rowptr[win_rows], dtype=np.int32)  # edges before each window
+    if window_weight is None:
+        win_rows = np.minimum(np.arange(n_rw + 1, dtype=np.int64) * 16, num_nodes)
+        prefix = np.ascontiguousarray(rowptr[win_rows], dtype=np.int32)  # edges before each window
+    else:
+        assert window_weight.shape[0] == n_rw
+        prefix = np.zeros(n_rw + 1, dtype=np.int64)
+        np.cumsum(window_weight.astype(np.int64), out=prefix[1:])
+        assert prefix[-1] < 2**31
+        prefix = prefix.astype(np.int32)
     cuts_w = cabi.partition_row_windows(prefix, n_parts)
     return np.minimum(cuts_w.astype(np.int64) * 16, num_nodes)
 
@@ -58,6 +67,7 @@ class RowShard:
     colidx: np.ndarray  # int32, GLOBAL column ids
     row_cuts: np.ndarray
     max_rows: int       # largest row block of any rank
+    local_last: bool = False  # number the rank's own columns after everybody else's (see padded_colidx)
 
     @property
     def num_rows(self) -> int:
@@ -68,26 +78,46 @@ class RowShard:
         return int(self.colidx.shape[0])
 
     @property
-    def padded_cols(self) -> int:
+    def gathered_rows(self) -> int:
+        """Rows of the all-gather's output: ``world`` blocks of ``max_rows``."""
         return self.world * self.max_rows
 
+    @property
+    def col_split(self) -> int:
+        """With ``local_last``: column ids at or above this value are the rank's own rows."""
+        return self.world * self.max_rows
+
+    @property
+    def padded_cols(self) -> int:
+        """Rows of the buffer the kernel gathers from: the ``world`` gathered blocks and, with
+        ``local_last``, one more block that holds the rank's own rows (it doubles as the send buffer of
+        the all-gather)."""
+        return (self.world + (1 if self.local_last and self.world > 1 else 0)) * self.max_rows
+
     def padded_colidx(self) -> np.ndarray:
-        """Column ids in the padded gather layout (monotone in the global id, so sortedness and
-        the TC-block structure are unchanged)."""
+        """Column ids in the padded gather layout: a row of rank s sits at ``s*max_rows + i``, where the
+        all-gather puts it (monotone in the global id, so sortedness and the TC-block structure are
+        unchanged).  With ``local_last`` the rank's own rows are numbered ``world*max_rows + i`` instead
+        -- the send buffer itself, which follows the gathered blocks -- so a window's own columns are the
+        tail of its column list: what the fused kernel can work on before the all-gather has finished."""
         if self.world == 1:
             return self.colidx
         owner = np.searchsorted(self.row_cuts, self.colidx, side="right") - 1
         local = self.colidx.astype(np.int64) - self.row_cuts[owner]
-        return (owner.astype(np.int64) * self.max_rows + local).astype(np.int32)
+        block = owner.astype(np.int64)
+        if self.local_last:
+            block = np.where(owner == self.rank, self.world, block)
+        return (block * self.max_rows + local).astype(np.int32)
 
 
-def make_shard(rowptr: np.ndarray, colidx: np.ndarray, num_nodes: int, rank: int, world: int) -> RowShard:
-    cuts = partition_rows(rowptr, num_nodes, world)
+def make_shard(rowptr: np.ndarray, colidx: np.ndarray, num_nodes: int, rank: int, world: int,
+               window_weight: np.ndarray | None = None, local_last: bool = False) -> RowShard:
+    cuts = partition_rows(rowptr, num_nodes, world, window_weight)
     r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
     e0, e1 = int(rowptr[r0]), int(rowptr[r1])
     local_ptr = (rowptr[r0 : r1 + 1].astype(np.int64) - e0).astype(np.int32)
     return RowShard(rank, world, r0, r1, num_nodes, local_ptr, np.ascontiguousarray(colidx[e0:e1]), cuts,
-                    int(np.max(np.diff(cuts))))
+                    int(np.max(np.diff(cuts))), local_last)
 
 
 def all_gather_padded(local_padded, full_padded, group=None):
@@ -133,10 +163,17 @@ def all_gather_rows(local, row_cuts, full=None, group=None):
 class ShardedAttention:
     """Fused sparse attention on this rank's block of rows (row-window sharding).
 
-    ``forward_fn(tcb, num_rows, q_local, k_full, v_full, scale_divisor) -> out_local`` defaults
-    to the CUDA path; the CPU tests substitute a checker so that the partition / gather logic
-    can run under gloo without a GPU.  ``k_full``/``v_full`` are in the padded gather layout and
-    the column ids the kernel sees are renumbered accordingly."""
+    K and V rows of a node are kept side by side in ONE buffer (``[rows, 2, H, d]``: the kernel takes a
+    row stride, so the interleaving costs nothing), which makes the exchange one collective instead of
+    two.  ``send_buffers`` hands out the views a producer writes its K / V rows into.
+
+    With a ``local_last`` shard and more than one rank, ``forward`` overlaps the all-gather with compute:
+    the collective runs on a side stream while the first kernel launch works on the columns the rank
+    already holds (its own rows); the second launch waits for the collective's event and does the rest.
+    No kernel reads another GPU's memory and nothing spins on a flag: two launches and one event.
+
+    ``forward_fn(tcb, num_rows, q_local, k_full, v_full, scale_divisor) -> out_local`` replaces the CUDA
+    path in the CPU tests, so that the partition / gather logic can run under gloo without a GPU."""
 
     def __init__(self, shard: RowShard, device, block_w: int = 16, forward_fn=None, preprocess_fn=None, tcb=None):
         import torch
@@ -153,38 +190,57 @@ class ShardedAttention:
             self.tcb = cabi.preprocess(ci, rp, shard.num_rows, block_w, num_cols=shard.padded_cols)
         else:
             self.tcb = preprocess_fn(shard)
-        self._k_full = None
-        self._v_full = None
-        self._k_send = None
-        self._v_send = None
+        self._kv = None       # [padded_cols, 2, ...]: gathered blocks (+ the own block when local_last)
+        self._send = None     # [max_rows, 2, ...]: what this rank contributes to the all-gather
         self._plan = None
+        self._phased = None
+        self._comm_stream = None
+        self.two_phase = bool(shard.local_last and shard.world > 1 and forward_fn is None)
+
+    # views of the interleaved buffers
+    @property
+    def _k_full(self):
+        return self._kv[:, 0]
+
+    @property
+    def _v_full(self):
+        return self._kv[:, 1]
 
     def _buffers(self, like):
         import torch
 
         s = self.shard
         tail = tuple(like.shape[1:])
-        if self._k_full is None or tuple(self._k_full.shape[1:]) != tail or self._k_full.dtype != like.dtype:
-            mk = lambda rows: torch.zeros((rows,) + tail, dtype=like.dtype, device=like.device)
-            self._k_full, self._v_full = mk(s.padded_cols), mk(s.padded_cols)
-            self._k_send, self._v_send = mk(s.max_rows), mk(s.max_rows)
-            self._plan = None
+        if self._kv is None or tuple(self._kv.shape[2:]) != tail or self._kv.dtype != like.dtype:
+            self._kv = torch.zeros((s.padded_cols, 2) + tail, dtype=like.dtype, device=like.device)
+            if s.local_last and s.world > 1:  # the own block follows the gathered ones and is the send buffer
+                self._send = self._kv[s.gathered_rows:]
+            else:
+                self._send = torch.zeros((s.max_rows, 2) + tail, dtype=like.dtype, device=like.device)
+            self._plan = self._phased = None
 
     def send_buffers(self, like):
-        """Persistent ``[max_rows, ...]`` buffers a caller may write its K/V rows into directly
+        """Persistent ``[max_rows, ...]`` views (K, V) a caller may write its K / V rows into directly
         (rows beyond its block stay zero); passing them to ``forward`` skips one local copy."""
         self._buffers(like)
-        return self._k_send, self._v_send
+        return self._send[:, 0], self._send[:, 1]
 
-    def gather_kv(self, k_local, v_local):
+    def _stage(self, k_local, v_local):
         self._buffers(k_local)
         n = self.shard.num_rows
-        if k_local.data_ptr() != self._k_send.data_ptr():
-            self._k_send[:n].copy_(k_local[:n])
-        if v_local.data_ptr() != self._v_send.data_ptr():
-            self._v_send[:n].copy_(v_local[:n])
-        all_gather_padded(self._k_send, self._k_full)
-        all_gather_padded(self._v_send, self._v_full)
+        if k_local.data_ptr() != self._send[:, 0].data_ptr():
+            self._send[:n, 0].copy_(k_local[:n])
+        if v_local.data_ptr() != self._send[:, 1].data_ptr():
+            self._send[:n, 1].copy_(v_local[:n])
+
+    def _all_gather(self):
+        s = self.shard
+        all_gather_padded(self._send, self._kv[: s.gathered_rows])
+
+    def gather_kv(self, k_local, v_local):
+        """All-gather (one collective for K and V); returns the K and V views the kernel indexes."""
+        self._stage(k_local, v_local)
+        self._all_gather()
         return self._k_full, self._v_full
 
     def forward_local(self, q_local, k_full, v_full, scale_divisor: float = 1.0):
@@ -192,16 +248,41 @@ class ShardedAttention:
         if self.forward_fn is not None:
             return self.forward_fn(self.tcb, self.shard.num_rows, q_local, k_full, v_full, scale_divisor)
         p = self._plan
-        if p is None or p.q is not q_local or p.k is not k_full or p.v is not v_full or p.scale_divisor != scale_divisor:
+        if p is None or p.q is not q_local or p.k.data_ptr() != k_full.data_ptr() or \
+                p.v.data_ptr() != v_full.data_ptr() or p.scale_divisor != scale_divisor:
             p = cabi.ForwardPlan(self.tcb, self.shard.num_rows, q_local, k_full, v_full, scale_divisor)
             self._plan = p
         p.launch()
         return p.out
 
     def forward(self, q_local, k_local, v_local, scale_divisor: float = 1.0):
-        """All-gather K/V rows, then run the fused kernel on the local rows."""
-        k_full, v_full = self.gather_kv(k_local, v_local)
-        return self.forward_local(q_local, k_full, v_full, scale_divisor)
+        """All-gather K/V rows and run the fused kernel on the local rows; with a ``local_last`` shard
+        the kernel's first launch (own columns) runs while the collective is in flight."""
+        if not self.two_phase:
+            k_full, v_full = self.gather_kv(k_local, v_local)
+            return self.forward_local(q_local, k_full, v_full, scale_divisor)
+        import torch
+
+        self._stage(k_local, v_local)
+        p = self._phased
+        if p is None or p.q is not q_local or p.scale_divisor != float(scale_divisor):
+            p = cabi.PhasedForwardPlan(self.tcb, self.shard.num_rows, q_local, self._k_full, self._v_full,
+                                       scale_divisor, self.shard.col_split)
+            self._phased = p
+        if self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=self.device)
+        cur = torch.cuda.current_stream(self.device)
+        self._comm_stream.wait_stream(cur)  # the K / V rows of this step have been written
+        with torch.cuda.stream(self._comm_stream):
+            self._all_gather()
+            arrived = torch.cuda.Event()
+            arrived.record(self._comm_stream)
+        p.launch_phase(1)          # columns this rank owns: reads only the send block
+        cur.wait_event(arrived)
+        p.launch_phase(2)          # everybody else's columns, continuing from phase 1's state
+        # the next step's K / V may overwrite the send block only after the collective has read it; the
+        # wait above already orders every later operation of this stream behind the collective
+        return p.out
 
 
 class HeadShardedAttention:
@@ -281,6 +362,208 @@ class HeadShardedAttention:
         v = self._rows_to_heads(v_rows)
         out = self.forward_resident(q, k, v, scale_divisor)
         return self._heads_to_rows(out)
+
+
+def _all_to_all(recv, send, group=None):
+    """``recv[j]`` <- rank j's ``send[this rank]`` (equal blocks along dim 0); a copy without a process group."""
+    import torch.distributed as dist
+
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        recv.copy_(send)
+    else:
+        dist.all_to_all_single(recv, send, group=group)
+
+
+class HeadShardedPipeline:
+    """Heads over the ranks with row-sharded producers and consumers, pipelined.
+
+    Every rank owns a block of rows (cut on 16-row boundaries) of Q, K, V and of the output, all heads;
+    it computes all rows for ``heads/world`` heads.  Per call:
+
+        exchange stream:  K+V all-to-all | Q chunk 0 | Q chunk 1 | ... | out chunk 0 | out chunk 1 | ...
+        compute stream :                  (K+V, Q0) kernel 0 | kernel 1 | ...
+
+    The rows are cut into ``chunks`` pieces that each hold the same share of EVERY rank's block (so each
+    piece's all-to-all loads all links evenly); piece c has its own TC-block plan.  The kernel of piece c
+    needs K and V complete but only its own Q rows, and its output leaves while piece c+1 is computed.
+    K and V travel in one collective; the buffers on both sides of every collective are laid out so that
+    neither the kernel nor the collective needs a transposing copy ("exchange layout"):
+
+        q_x   [chunks, world(dest head group), seg, heads/world, d]     rows of piece c of this rank
+        kv_x  [world(dest head group), 2 (K, V), chunks*seg, heads/world, d]
+        out_x [chunks, world(source head group), seg, heads/world, d]   fp32
+
+    ``to_exchange_layout`` / ``kv_to_exchange_layout`` / ``from_exchange_layout`` convert from and to
+    ``[rows, heads, d]`` for callers that do not produce these layouts directly (a projection GEMM can:
+    they are strided-batched outputs).  The reference is single-GPU; no counterpart there."""
+
+    def __init__(self, rowptr: np.ndarray, colidx: np.ndarray, num_nodes: int, heads: int, rank: int, world: int,
+                 device, chunks: int = 4, block_w: int = 16, forward_fn=None):
+        import torch
+
+        assert heads % world == 0, "head sharding needs heads divisible by the number of ranks"
+        self.n, self.heads, self.rank, self.world = num_nodes, heads, rank, world
+        self.hl = heads // world
+        self.device = torch.device(device)
+        self.forward_fn = forward_fn
+        self.block_w = block_w
+        n_rw = (num_nodes + 15) // 16
+        self.cuts = np.minimum(np.round(np.arange(world + 1) * n_rw / world).astype(np.int64) * 16, num_nodes)
+        self.row_begin, self.row_end = int(self.cuts[rank]), int(self.cuts[rank + 1])
+        max_rows = int(np.max(np.diff(self.cuts)))
+        self.chunks = max(1, min(chunks, (max_rows + 15) // 16))
+        self.seg = ((max_rows + self.chunks - 1) // self.chunks + 15) // 16 * 16
+        self.rows_p = self.seg * self.chunks            # padded rows per rank
+        self.num_cols = world * 2 * self.rows_p          # K of rank s at s*2*rows_p + i, V rows_p further on
+        self._build_plans(rowptr, colidx)
+        self._bufs = None
+        self._comm = None
+        self._fwd = {}
+
+    def _build_plans(self, rowptr, colidx):
+        import torch
+
+        w, seg, cuts = self.world, self.seg, self.cuts
+        ptr = rowptr.astype(np.int64)
+        self.plans, self.n_tcb, self.preprocess_ms = [], 0, 0.0
+        for c in range(self.chunks):
+            deg = np.zeros(w * seg, dtype=np.int64)
+            pieces = []
+            for j in range(w):
+                a = min(int(cuts[j]) + c * seg, int(cuts[j + 1]))
+                b = min(a + seg, int(cuts[j + 1]))
+                deg[j * seg:j * seg + (b - a)] = np.diff(ptr[a:b + 1])
+                pieces.append(colidx[ptr[a]:ptr[b]])
+            cols = np.concatenate(pieces).astype(np.int64) if pieces else np.zeros(0, np.int64)
+            owner = np.searchsorted(cuts, cols, side="right") - 1
+            cols = (owner * 2 * self.rows_p + (cols - cuts[owner])).astype(np.int32)
+            rp = np.zeros(w * seg + 1, dtype=np.int64)
+            np.cumsum(deg, out=rp[1:])
+            rp = rp.astype(np.int32)
+            if self.forward_fn is not None:
+                self.plans.append((rp, cols))
+                continue
+            with torch.cuda.device(self.device):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                tcb = cabi.preprocess(torch.from_numpy(cols).to(self.device), torch.from_numpy(rp).to(self.device),
+                                      w * seg, self.block_w, num_cols=self.num_cols)
+                e1.record()
+                e1.synchronize()
+                self.preprocess_ms += e0.elapsed_time(e1)
+            self.n_tcb += tcb["nTCB"]
+            self.plans.append(tcb)
+
+    # ---- layouts
+    def _pad_rows(self, x_rows):
+        import torch
+
+        rows = self.row_end - self.row_begin
+        assert x_rows.shape[0] == rows
+        if rows == self.rows_p:
+            return x_rows
+        pad = torch.zeros((self.rows_p,) + tuple(x_rows.shape[1:]), dtype=x_rows.dtype, device=x_rows.device)
+        pad[:rows] = x_rows
+        return pad
+
+    def to_exchange_layout(self, q_rows):
+        """``[rows, heads, d]`` of this rank -> ``q_x`` ``[chunks, world, seg, heads/world, d]``."""
+        d = q_rows.shape[-1]
+        x = self._pad_rows(q_rows).view(self.chunks, self.seg, self.world, self.hl, d)
+        return x.permute(0, 2, 1, 3, 4).contiguous()
+
+    def kv_to_exchange_layout(self, k_rows, v_rows):
+        """Two ``[rows, heads, d]`` -> ``kv_x`` ``[world, 2, chunks*seg, heads/world, d]``."""
+        import torch
+
+        d = k_rows.shape[-1]
+        kv = torch.stack([self._pad_rows(k_rows), self._pad_rows(v_rows)], dim=0)  # [2, rows_p, H, d]
+        return kv.view(2, self.rows_p, self.world, self.hl, d).permute(2, 0, 1, 3, 4).contiguous()
+
+    def from_exchange_layout(self, out_x):
+        """``out_x`` ``[chunks, world, seg, heads/world, d]`` -> ``[rows, heads, d]`` of this rank."""
+        d = out_x.shape[-1]
+        y = out_x.permute(0, 2, 1, 3, 4).reshape(self.rows_p, self.heads, d)
+        return y[: self.row_end - self.row_begin]
+
+    def describe(self) -> str:
+        return (f"{self.hl} of {self.heads} heads per GPU; row-sharded producers/consumers in exchange layout; per step: "
+                f"one all-to-all for K+V, {self.chunks} for Q pieces, {self.chunks} kernel launches, {self.chunks} "
+                "all-to-alls for output pieces; the exchange of a piece overlaps the kernel of its neighbours")
+
+    def _buffers(self, q_x):
+        import torch
+
+        if self._bufs is None or self._bufs["q"].dtype != q_x.dtype or self._bufs["q"].shape != q_x.shape:
+            d = q_x.shape[-1]
+            dev = q_x.device
+            self._bufs = {
+                "q": torch.empty_like(q_x),  # [chunks, world(src), seg, hl, d]: piece c = rows of every rank
+                "kv": torch.empty((self.world, 2, self.rows_p, self.hl, d), dtype=q_x.dtype, device=dev),
+                "out_send": torch.empty((self.chunks, self.world, self.seg, self.hl, d), dtype=torch.float32, device=dev),
+                "out": torch.empty((self.chunks, self.world, self.seg, self.hl, d), dtype=torch.float32, device=dev),
+            }
+            self._fwd = {}
+        return self._bufs
+
+    def _kernel(self, c: int, scale_divisor: float):
+        """Launch the fused kernel of piece c on the current stream (inputs as the exchange left them)."""
+        b = self._bufs
+        d = b["q"].shape[-1]
+        q = b["q"][c].view(self.world * self.seg, self.hl, d)
+        kv = b["kv"].view(self.world * 2 * self.rows_p, self.hl, d)
+        k, v = kv, kv[self.rows_p:]  # a V row sits rows_p rows behind its K row
+        out = b["out_send"][c].view(self.world * self.seg, self.hl, d)
+        if self.forward_fn is not None:
+            out.copy_(self.forward_fn(self.plans[c], self.world * self.seg, q, k, v, scale_divisor))
+            return
+        key = (c, float(scale_divisor))
+        p = self._fwd.get(key)
+        if p is None:
+            p = cabi.ForwardPlan(self.plans[c], self.world * self.seg, q, k, v, scale_divisor, out=out)
+            self._fwd[key] = p
+        p.launch()
+
+    def kernel_only(self, scale_divisor: float = 8.0):
+        """The kernels of all pieces back to back, no exchange (inputs as the last ``forward`` left them)."""
+        for c in range(self.chunks):
+            self._kernel(c, scale_divisor)
+
+    def forward(self, q_x, kv_x, scale_divisor: float = 1.0):
+        """``q_x``, ``kv_x`` in exchange layout (fp16) -> ``out_x`` in exchange layout (fp32, a buffer that
+        the next call overwrites)."""
+        import torch
+
+        b = self._buffers(q_x)
+        if self.device.type != "cuda":  # CPU tests: same data movement, no streams
+            _all_to_all(b["kv"], kv_x)
+            for c in range(self.chunks):
+                _all_to_all(b["q"][c], q_x[c])
+                self._kernel(c, scale_divisor)
+                _all_to_all(b["out"][c], b["out_send"][c])
+            return b["out"]
+        if self._comm is None:
+            self._comm = torch.cuda.Stream(device=self.device)
+        cur, comm = torch.cuda.current_stream(self.device), self._comm
+        comm.wait_stream(cur)  # inputs written, previous call's kernels done with the buffers
+        q_ready = []
+        with torch.cuda.stream(comm):
+            _all_to_all(b["kv"], kv_x)
+            for c in range(self.chunks):
+                _all_to_all(b["q"][c], q_x[c])
+                ev = torch.cuda.Event()
+                ev.record(comm)
+                q_ready.append(ev)
+        for c in range(self.chunks):
+            cur.wait_event(q_ready[c])  # K+V were exchanged before any Q piece on the same stream
+            self._kernel(c, scale_divisor)
+            done = torch.cuda.Event()
+            done.record(cur)
+            with torch.cuda.stream(comm):
+                comm.wait_event(done)
+                _all_to_all(b["out"][c], b["out_send"][c])
+        cur.wait_stream(comm)
+        return b["out"]
 
 
 # ---------------------------------------------------------------------------------------------------

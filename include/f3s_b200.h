@@ -174,6 +174,59 @@ int f3s_forward_traced(const int32_t *row_window_offset, const int32_t *sorted_r
                        uint64_t *sm_trace, f3s_stream_t stream);
 
 /*
+ * Repeated calls on one graph.  f3s_forward schedules the row windows (a memset and a small kernel)
+ * before every launch, as the reference re-derives its launch geometry on every call
+ * (src/F3S_kernel.cu:581-612).  A caller that runs the same graph many times (every layer and step of
+ * a model) can schedule once and then pay one kernel launch per call:
+ *   f3s_forward_plan:    fills `workspace` (f3s_forward_workspace_bytes bytes, 256-byte aligned) with the
+ *                        schedule for (row_window_offset, sorted_row_windows, heads, head_dim).
+ *   f3s_forward_planned: the fused kernel alone, on a workspace prepared by f3s_forward_plan with the same
+ *                        sizes.  The kernel leaves the scratch ready for the next call.  Beyond f3s_forward:
+ *                        k and v have their own row stride ld_kv (for instance K and V rows interleaved in one
+ *                        gathered buffer), and the output may be fp16 (out_is_half).  No score dump.
+ * Calls that share a workspace must not overlap on the GPU.  After a call whose status
+ * (f3s_forward_status) is not F3S_OK the workspace must be planned again.
+ */
+int f3s_forward_plan(const int32_t *row_window_offset, const int32_t *sorted_row_windows, int32_t num_nodes,
+                     int32_t n_row_windows, int64_t n_tcb, int32_t block_w, int32_t heads, int32_t head_dim,
+                     void *workspace, size_t workspace_bytes, f3s_stream_t stream);
+int f3s_forward_planned(const int32_t *row_window_offset, const int32_t *sorted_row_windows,
+                        const int32_t *sparse_a_to_x_idx, const uint64_t *tcb_bitmap, int32_t num_nodes,
+                        int32_t n_row_windows, int64_t n_tcb, int32_t block_w, int32_t heads, int32_t head_dim,
+                        int64_t ld_q, const void *q, int64_t ld_kv, const void *k, const void *v,
+                        float scale_divisor, int32_t apply_softmax, void *out, int32_t out_is_half, void *workspace,
+                        size_t workspace_bytes, f3s_stream_t stream);
+
+/*
+ * Two-phase forward for row-sharded attention (no reference counterpart: the reference is single-GPU).
+ * A rank that owns a block of rows holds its own K / V rows before the step and receives the others'
+ * through a collective.  Phase 1 works on the columns with id >= col_split (by convention the rank's
+ * own rows, which the caller numbers last) and can run while the collective is in flight; phase 2 works
+ * on the columns with id < col_split, continues from the unnormalised result phase 1 left in the scratch
+ * (running max, running sum, accumulator per row) and writes the output.  Together they compute exactly
+ * what f3s_forward computes (same masking and softmax; the order of accumulation differs).
+ *   phase_split[n_row_windows]: for every window the index (into the TC-block arrays) of its first TC
+ *       block whose first column id is >= col_split, or row_window_offset[w+1] if it has none.  The block
+ *       before it is the only one that may hold columns of both kinds; both phases visit it, each masking
+ *       the other's columns.
+ *   workspace: f3s_forward_phased_workspace_bytes(...) bytes, 256-byte aligned, prepared once per graph
+ *       by f3s_forward_phased_plan; then any number of (phase 1, phase 2) pairs.  `out` may be NULL in
+ *       phase 1.  head_dim must be 64; softmax is always applied.
+ */
+size_t f3s_forward_phased_workspace_bytes(int32_t n_row_windows, int64_t n_tcb, int32_t block_w, int32_t heads,
+                                          int32_t head_dim);
+int f3s_forward_phased_plan(const int32_t *row_window_offset, const int32_t *sorted_row_windows,
+                            const int32_t *phase_split, int32_t num_nodes, int32_t n_row_windows, int64_t n_tcb,
+                            int32_t block_w, int32_t heads, int32_t head_dim, void *workspace,
+                            size_t workspace_bytes, f3s_stream_t stream);
+int f3s_forward_phase(int32_t phase, const int32_t *row_window_offset, const int32_t *sorted_row_windows,
+                      const int32_t *sparse_a_to_x_idx, const uint64_t *tcb_bitmap, const int32_t *phase_split,
+                      int32_t col_split, int32_t num_nodes, int32_t n_row_windows, int64_t n_tcb, int32_t block_w,
+                      int32_t heads, int32_t head_dim, int64_t ld_q, const void *q, int64_t ld_kv, const void *k,
+                      const void *v, float scale_divisor, float *out, void *workspace, size_t workspace_bytes,
+                      f3s_stream_t stream);
+
+/*
  * Device-side error reporting.  The reference's kernels report nothing and its host code ends the
  * process on any CUDA error (printf + exit(-1), src/F3S_kernel.cu:662-666); here a kernel that cannot
  * finish its work writes a status word into the scratch of the call and returns, and the host reads it.

@@ -114,7 +114,7 @@ def test_cfg5_fullsize_forward_all_heads(cfg5):
     # a head of the multi-head call against the one-head call on that head's (strided) slices
     for h in (0, 5):
         one = cabi.forward(tcb, n, qd[:, h], kd[:, h], vd[:, h], 8.0)
-        assert torch.allclose(one, out[:, h], rtol=1e-4, atol=1e-5)
+        assert torch.allclose(one, out[:, h], rtol=2e-3, atol=5e-4)
     # oracle on sampled (head, row block) pairs, among them the rows of the largest window
     rng = np.random.default_rng(6)
     big = int(tcb["sortedRowWindows"][0]) * 16

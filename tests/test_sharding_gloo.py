@@ -116,6 +116,57 @@ def test_two_rank_head_sharded_forward_equals_single(tmp_path):
     assert torch.load(out_file)["ok"]
 
 
+def _pipeline_worker(rank, world, port, rowptr, colidx, n, heads, chunks, out_file):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        gen = torch.Generator().manual_seed(11)
+        q, k, v = (torch.randn((n, heads, 16), generator=gen).half() for _ in range(3))
+        full = ao.edge_attention(rowptr, colidx, q, k, v, 4.0)
+        fn = lambda plan, rows, qq, kk, vv, sc: ao.edge_attention(plan[0], plan[1], qq, kk, vv, sc)
+        hp = sharding.HeadShardedPipeline(rowptr, colidx, n, heads, rank, world, "cpu", chunks=chunks, forward_fn=fn)
+        assert hp.row_begin % 16 == 0 and hp.seg % 16 == 0
+        rb, re_ = hp.row_begin, hp.row_end
+        q_x = hp.to_exchange_layout(q[rb:re_])
+        kv_x = hp.kv_to_exchange_layout(k[rb:re_], v[rb:re_])
+        # the layouts round-trip
+        assert torch.equal(hp.from_exchange_layout(q_x.float()), q[rb:re_].float())
+        for _ in range(2):
+            out = hp.from_exchange_layout(hp.forward(q_x, kv_x, 4.0))
+            assert out.shape == (re_ - rb, heads, 16)
+            assert torch.allclose(out, full[rb:re_], rtol=1e-6, atol=1e-6)
+        if rank == 0:
+            torch.save({"ok": True}, out_file)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n,heads,chunks", [(256, 4, 2), (301, 2, 3)])
+def test_two_rank_head_sharded_pipeline_equals_single(tmp_path, n, heads, chunks):
+    rowptr, colidx = random_csr(n, 9, 16)
+    out_file = str(tmp_path / "res.pt")
+    mp.spawn(_pipeline_worker, args=(2, _free_port(), rowptr, colidx, n, heads, chunks, out_file), nprocs=2, join=True)
+    assert torch.load(out_file)["ok"]
+
+
+def test_local_last_numbering_splits_own_and_other_columns():
+    rowptr, colidx = random_csr(500, 12, 3)
+    for r in range(3):
+        s = sharding.make_shard(rowptr, colidx, 500, r, 3, local_last=True)
+        pc = s.padded_colidx().astype(np.int64)
+        own = (s.colidx >= s.row_begin) & (s.colidx < s.row_end)
+        assert pc.max() < s.padded_cols == 4 * s.max_rows
+        assert np.all(pc[own] >= s.col_split) and np.all(pc[~own] < s.col_split)
+        # other ranks' columns keep their order; own columns keep theirs
+        assert np.array_equal(np.argsort(pc[~own], kind="stable"), np.argsort(s.colidx[~own], kind="stable"))
+        assert np.array_equal(np.argsort(pc[own], kind="stable"), np.argsort(s.colidx[own], kind="stable"))
+    w = np.ones((500 + 15) // 16, dtype=np.int64)
+    w[:4] = 50  # heavy first windows: the cut moves forward
+    cuts = sharding.partition_rows(rowptr, 500, 2, window_weight=w)
+    assert cuts[1] < sharding.partition_rows(rowptr, 500, 2)[1]
+
+
 def test_padded_column_ids_are_monotone():
     rowptr, colidx = random_csr(500, 12, 3)
     for r in range(3):
