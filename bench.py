@@ -60,6 +60,15 @@ def parse_args():
     ap.add_argument("--e2e-chunks", type=int, default=4, help="row chunks of the host-to-host pipeline")
     ap.add_argument("--head-chunks", type=int, default=4,
                     help="row chunks of the head-sharded pipeline (kernel of one chunk overlaps the exchange of others)")
+    ap.add_argument("--two-phase", action="store_true",
+                    help="multi-GPU row sharding: overlap the all-gather with a first kernel launch on the rank's own "
+                         "columns (default: collective, then one launch)")
+    ap.add_argument("--reserve-sms", type=int, default=32,
+                    help="multi-GPU, overlapped schemes (head pipeline, --two-phase): SMs the fused kernel leaves to the "
+                         "collectives' kernels while both run")
+    ap.add_argument("--nccl-max-ctas", type=int, default=32,
+                    help="multi-GPU, overlapped schemes: cap on NCCL's CTAs per collective in the process group those "
+                         "schemes use (0: NCCL's default); the plain all-gather of row sharding is never capped")
     ap.add_argument("--reorder", default="none", choices=["none", "degree"],
                     help="relabel the nodes before building TC blocks (fused3s_b200.reorder); the default "
                          "benchmark keeps the generator's order")
@@ -162,8 +171,9 @@ def sharding_note(args, heads):
     if mode == "auto" or heads % args.gpus != 0:
         mode = "heads" if (args.sharding == "auto" and heads > 1 and heads % args.gpus == 0) else "rows"
     if mode == "rows":
-        return ("row windows by TC-block count; K and V all-gathered by one NCCL collective inside every step, "
-                "overlapped with the kernel launch that works on the rank's own columns")
+        return ("row windows by TC-block count; K and V all-gathered by one NCCL collective inside every step" +
+                (", overlapped with a first kernel launch on the rank's own columns" if args.two_phase else
+                 ", then one kernel launch"))
     if mode == "heads-resident":
         return f"{heads // args.gpus} of {heads} heads per GPU, Q/K/V already head-sharded: no communication"
     return (f"{heads // args.gpus} of {heads} heads per GPU; row-sharded Q/K/V -> all-to-all (K+V in one, Q by row "
@@ -316,25 +326,37 @@ def parity_check(g, q_h, k_h, v_h, out, row_begin, row_end, seed, blocks=4):
     return ok, worst_abs, worst_rel
 
 
-def roofline_record(b_alg, b_min, kern_ms, peak, peak_src, traffic, kv_bytes, l2_gather_gbs, gather_bytes, kernel):
-    """The HBM fraction the contract asks for, and -- when K + V fit the L2 cache, so that the gathers never
-    reach DRAM -- the fraction of the L2 gather rate measured by this package's own probe kernel."""
+def roofline_record(b_alg, b_min, kern_ms, peak, peak_src, traffic, kv_bytes, l2_gather_gbs, gather_bytes, kernel,
+                    hbm_gather_gbs=None):
+    """The HBM fraction the contract asks for, plus the two measured ceilings that actually bind a gather
+    kernel: this package's probe kernel gathers 128-byte rows at random ids from a table of the size of
+    K + V (L2-resident case) and from a 4 GiB table (HBM case).  ``frac_mixed`` compares the kernel time with
+    gathered bytes / gather ceiling + streamed bytes (Q, output, metadata) / copy rate."""
     achieved = b_alg / (kern_ms * 1e-3) / 1e9
     rec = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
            "traffic": traffic, "peak_source": peak_src, "algorithmic_bytes_per_call": b_alg, "kernel": kernel,
            "frac_dram_compulsory": b_min / (kern_ms * 1e-3) / 1e9 / peak,
-           "compulsory_bytes_per_call": b_min}
+           "compulsory_bytes_per_call": b_min, "gathered_bytes_per_call": gather_bytes}
     l2_resident = kv_bytes < 100e6
     rec["bound_effective"] = "l2" if l2_resident else "hbm"
     if l2_gather_gbs is not None:
         rec["l2_peak_gbs"] = l2_gather_gbs
         rec["frac_l2"] = gather_bytes / (kern_ms * 1e-3) / 1e9 / l2_gather_gbs
-        rec["l2_peak_source"] = ("f3s_probe_gather_rows: 128-byte rows at random ids from a table of the size of "
-                                 "K + V, loads only, best of 5, same process")
-    rec["note"] = ("frac = algorithmic bytes / kernel time / measured HBM copy rate; with K + V inside the L2 cache the "
-                   "gathers are served from L2 and frac may exceed 1: frac_l2 (gathered K/V bytes over the measured "
-                   "L2 gather rate) is then the fraction of the binding roof" if l2_resident else
-                   "K + V exceed the L2 cache: the gathers run from HBM and frac is the fraction of the binding roof")
+    if hbm_gather_gbs is not None:
+        rec["hbm_gather_peak_gbs"] = hbm_gather_gbs
+    ceiling = l2_gather_gbs if l2_resident else hbm_gather_gbs
+    if ceiling:
+        t_roof = gather_bytes / ceiling / 1e6 + (b_alg - gather_bytes) / peak / 1e6  # ms
+        rec["t_roof_mixed_ms"] = t_roof
+        rec["frac_mixed"] = t_roof / kern_ms
+    rec["gather_peak_source"] = ("f3s_probe_gather_rows (this package): 128-byte rows at seeded random ids, loads only, "
+                                 "best of 5, same process; table = size of K + V of one head (L2) / 4 GiB (HBM)")
+    rec["note"] = ("frac = algorithmic bytes / kernel time / measured HBM copy rate. K + V of a head fit the L2 cache, so "
+                   "the gathers never reach DRAM and frac may exceed 1; frac_l2 and frac_mixed (against the measured L2 "
+                   "gather rate) say how far the kernel is from the roof that binds" if l2_resident else
+                   "frac = algorithmic bytes / kernel time / measured HBM copy rate. K + V of a head exceed the L2 cache; "
+                   "random 128-byte rows come from HBM slower than a copy streams, hence frac_mixed against the measured "
+                   "HBM gather rate (above 1 when part of the gathers still hit L2)")
     return rec
 
 
@@ -465,12 +487,14 @@ def single_gpu_subrecord(bench, cfg, args, steps):
     peak, peak_src = measured_peaks()
     kv_bytes = 2 * n * d * 2  # K + V of ONE head: heads are processed one after the other by every warp
     l2 = cabi.gather_rate_gbs(kv_bytes, dev) if kv_bytes < 100e6 else None
+    hbm_g = cabi.gather_rate_gbs(4 << 30, dev, n_ids=1 << 23)
     t = float(ms.mean())
     rec = {"workload": workload_config(args, g)["workload"], "ms_per_step": t, "ms_per_step_median": float(np.median(ms)),
            "edge_gflops": 4.0 * d * heads * g.nnz / (t * 1e-3) / 1e9, "steps": steps, "gpu_launches": launches,
            "preprocess_ms": float(min(pre)), "tcb": {"nTCB": tcb["nTCB"], "sumU": sum_u, "nRW": n_rw},
            "roofline": roofline_record(b_alg, b_min, t, peak, peak_src, traffic_for(f"cfg{cfg}"), kv_bytes, l2,
-                                       heads * d * 4 * sum_u, kernel_name(d, tcb["nTCB"], n_rw, plan.ws_bytes <= 256))}
+                                       heads * d * 4 * sum_u, kernel_name(d, tcb["nTCB"], n_rw, plan.ws_bytes <= 256),
+                                       hbm_g)}
     if not args.no_ref_cuda:
         rec["reference_cuda_rebuilt"] = time_rebuilt_reference(tcb, n, qd, kd, vd)
     if not args.no_parity_check:
@@ -482,7 +506,7 @@ def single_gpu_subrecord(bench, cfg, args, steps):
     return rec
 
 
-def multi_gpu_heads_subrecord(bench, cfg, args, steps, rank, world):
+def multi_gpu_heads_subrecord(bench, cfg, args, steps, rank, world, group=None):
     """The multi-head workload with the heads divided over the ranks and row-sharded producers and
     consumers: the step holds the all-to-all of Q/K/V, the kernel and the all-to-all of the output."""
     import torch
@@ -496,7 +520,8 @@ def multi_gpu_heads_subrecord(bench, cfg, args, steps, rank, world):
     n, heads, d = g.num_nodes, g.heads, g.dim
     if heads % world != 0:
         return {"unavailable": f"{heads} heads do not divide over {world} GPUs"}
-    attn = sharding.HeadShardedPipeline(g.rowptr, g.colidx, n, heads, rank, world, dev, chunks=args.head_chunks)
+    attn = sharding.HeadShardedPipeline(g.rowptr, g.colidx, n, heads, rank, world, dev, chunks=args.head_chunks,
+                                        reserve_sms=args.reserve_sms, group=group)
     rb, re_ = attn.row_begin, attn.row_end
     q_x = attn.to_exchange_layout(q_h[rb:re_].to(dev))
     kv_x = attn.kv_to_exchange_layout(k_h[rb:re_].to(dev), v_h[rb:re_].to(dev))
@@ -534,6 +559,9 @@ def main():
 
     from fused3s_b200 import graphs
 
+    # torchrun pins every rank to one host thread; the seeded feature tensors are drawn on the host
+    torch.set_num_threads(max(1, (os.cpu_count() or 1) // max(1, world)))
+
     if args.impl == "reference":
         if rank != 0:
             return
@@ -549,8 +577,13 @@ def main():
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    overlap_group = None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        if args.nccl_max_ctas > 0:  # collectives that share the GPU with the fused kernel: a narrow communicator
+            opts = dist.ProcessGroupNCCL.Options()
+            opts.config.max_ctas = args.nccl_max_ctas
+            overlap_group = dist.new_group(ranks=list(range(world)), backend="nccl", pg_options=opts)
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     bench = Bench(dev, world)
     lib = cabi.lib()
@@ -608,7 +641,7 @@ def main():
         k_pin = k_h[r0:r1].contiguous().pin_memory()
         v_pin = v_h[r0:r1].contiguous().pin_memory()
         q_loc = q_pin.to(dev)
-        attn = sharding.ShardedAttention(shard, dev, 16, tcb=tcb)
+        attn = sharding.ShardedAttention(shard, dev, 16, tcb=tcb, two_phase=args.two_phase, reserve_sms=args.reserve_sms)
         if world > 1:  # the local K/V rows live in the send block of the all-gather
             k_loc, v_loc = attn.send_buffers(q_loc)
             k_loc[: r1 - r0].copy_(k_pin)
@@ -666,7 +699,8 @@ def main():
         # ---- heads divided over the ranks; every rank runs all row windows for heads/world heads
         rp_t = torch.from_numpy(g.rowptr).to(dev)
         ci_t = torch.from_numpy(g.colidx).to(dev)
-        hp = sharding.HeadShardedPipeline(g.rowptr, g.colidx, n, heads, rank, world, dev, chunks=args.head_chunks)
+        hp = sharding.HeadShardedPipeline(g.rowptr, g.colidx, n, heads, rank, world, dev, chunks=args.head_chunks,
+                                          reserve_sms=args.reserve_sms, group=overlap_group)
         preprocess_ms = hp.preprocess_ms
         n_tcb_local = hp.n_tcb
         sum_u_local = distinct_window_columns(rp_t, ci_t, n)
@@ -727,6 +761,15 @@ def main():
     else:
         ms_kernel, ms_kernel_local = ms_steps, ms_steps
     clocks = sampler.stop() if rank == 0 else None
+    if world > 1 and mode == "rows":  # the parts of the step, each timed alone
+        ms_ag, _ = bench.timed(attn._all_gather, args.steps)
+        parts = {"all_gather_alone_ms": float(ms_ag.mean())}
+        if attn._phased is not None:
+            ph = attn._phased
+            ms_2p, _ = bench.timed(lambda: (ph.launch_phase(1), ph.launch_phase(2)), args.steps)
+            parts["two_launches_without_collective_ms"] = float(ms_2p.mean())
+    else:
+        parts = None
     if world > 1:  # per-rank kernel time: how well the partition balances
         t = torch.tensor([float(ms_kernel_local.mean())], device=dev, dtype=torch.float64)
         allt = [torch.zeros_like(t) for _ in range(world)]
@@ -832,7 +875,7 @@ def main():
             others["cfg3"] = single_gpu_subrecord(bench, 3, args, sub_steps)
             others["cfg5"] = single_gpu_subrecord(bench, 5, args, sub_steps)
         else:
-            others["cfg5"] = multi_gpu_heads_subrecord(bench, 5, args, sub_steps, rank, world)
+            others["cfg5"] = multi_gpu_heads_subrecord(bench, 5, args, sub_steps, rank, world, overlap_group)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -848,8 +891,8 @@ def main():
     traffic = traffic_for(args.workload)
     roof = roofline_record(b_alg / world, b_min / world, kern_ms, peak, peak_src, traffic, kv_bytes, l2_gbs,
                            heads * d * 4 * sum_u / world,
-                           kernel_name(d, n_tcb_local, (out_range[1] - out_range[0] + 15) // 16, False))
-    roof["hbm_gather_peak_gbs"] = hbm_gather_gbs
+                           kernel_name(d, n_tcb_local, (out_range[1] - out_range[0] + 15) // 16, False),
+                           hbm_gather_gbs)
     roof["per_gpu"] = "bytes of one rank (1/n_gpus of the job) over the kernel-only time"
     line = {
         "metric": "edge_gflops", "value": flops / (ms * 1e-3) / 1e9, "unit": "GFLOP/s", "n_gpus": world,
@@ -873,6 +916,8 @@ def main():
         line["parity"] = parity
     if balance is not None:
         line["balance"] = balance
+    if parts is not None:
+        line["step_parts"] = parts
     if others is not None:
         line["other_workloads"] = others
     if training is not None:

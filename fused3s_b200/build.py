@@ -19,7 +19,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 INCLUDE = PKG.parent / "include"
 LIB = PKG / "libf3s_b200.so"
-CUDA_SOURCES = ["abi.cu", "forward.cu", "backward.cu", "preprocess.cu", "probe.cu"]
+CUDA_SOURCES = ["abi.cu", "forward.cu", "backward.cu", "preprocess.cu", "probe.cu", "sddmm_umma.cu"]
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

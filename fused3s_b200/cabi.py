@@ -39,6 +39,9 @@ EXPORTS = (
     "f3s_forward_phased_workspace_bytes",
     "f3s_forward_phased_plan",
     "f3s_forward_phase",
+    "f3s_set_max_ctas",
+    "f3s_set_canonical_chunk_tiles",
+    "f3s_sddmm_umma",
     "f3s_forward_status",
     "f3s_forward_static_status",
     "f3s_status_word_to_code",
@@ -115,6 +118,12 @@ def lib() -> C.CDLL:
         l.f3s_forward_phase.restype = C.c_int
         l.f3s_forward_phase.argtypes = [i32, vp, vp, vp, vp, vp, i32, i32, i32, i64, i32, i32, i32, i64, vp, i64, vp,
                                         vp, f32, vp, vp, sz, vp]
+        l.f3s_sddmm_umma.restype = C.c_int
+        l.f3s_sddmm_umma.argtypes = [vp, vp, vp, i32, i32, i64, i32, i32, i64, vp, i64, vp, vp, vp, sz, vp]
+        l.f3s_set_canonical_chunk_tiles.restype = None
+        l.f3s_set_canonical_chunk_tiles.argtypes = [i32]
+        l.f3s_set_max_ctas.restype = None
+        l.f3s_set_max_ctas.argtypes = [i32]
         l.f3s_forward_status.restype = C.c_int
         l.f3s_forward_status.argtypes = [vp, vp, vp]
         l.f3s_forward_static_status.restype = C.c_int
@@ -385,6 +394,29 @@ def window_tcb_counts(colidx, rowptr, num_nodes: int, block_w: int = 16):
                                      _ptr(e2r), _ptr(rwo), _ptr(ws), ws_bytes, C.byref(n_tcb), C.byref(max_tcb),
                                      _stream(dev)))
     return bp
+
+
+def sddmm_umma(tcb: dict, num_nodes: int, q, k, out=None):
+    """``f3s_sddmm_umma``: masked, unscaled score tiles ``[nTCB*block_w/8 * 128]`` fp32 computed with
+    tcgen05.mma / tensor memory (one head, head_dim 64).  Returns the tensor; raises if the kernel reported
+    a failed wait."""
+    import torch
+
+    bw = tcb["block_w"]
+    n_rw = tcb["rowWindowOffset"].numel() - 1
+    n_tcb = tcb["sparseAToXidx"].numel() // bw
+    dev = q.device
+    if q.dim() != 2 or k.dim() != 2:
+        raise F3SError(ERR_INVALID_ARG, "one head: q and k must be [N, 64]")
+    with torch.cuda.device(dev):
+        if out is None:
+            out = torch.empty(n_tcb * 16 * bw, dtype=torch.float32, device=dev)
+        ws = torch.empty(64, dtype=torch.uint8, device=dev)
+        check(lib().f3s_sddmm_umma(_ptr(tcb["rowWindowOffset"]), _ptr(tcb["sparseAToXidx"]), _ptr(tcb["tcbBitMap"]),
+                                   num_nodes, n_rw, n_tcb, bw, q.shape[-1], _ld(q, 1, q.shape[-1]), _ptr(q),
+                                   _ld(k, 1, k.shape[-1]), _ptr(k), _ptr(out), _ptr(ws), 64, _stream(dev)))
+        check(lib().f3s_forward_status(_ptr(ws), None, _stream(dev)))
+    return out
 
 
 def validate_plan(tcb: dict, num_kv_rows: int, scheduled: bool = True) -> None:

@@ -994,8 +994,15 @@ struct Geometry {
   size_t zero_bytes;  // header + arrival counters, cleared at the start of every scheduled call
 };
 
-constexpr int UNITS_PER_WARP = 6;
-constexpr int MIN_CH8 = 64;
+constexpr int UNITS_PER_WARP_DEFAULT = 6;
+constexpr int MIN_CH8_DEFAULT = 64;
+static int tuning(const char *name, int dflt) {  // experiment knobs, read once
+  const char *e = getenv(name);
+  const int v = e ? atoi(e) : 0;
+  return v > 0 ? v : dflt;
+}
+static const int UNITS_PER_WARP = tuning("F3S_UNITS_PER_WARP", UNITS_PER_WARP_DEFAULT);
+static const int MIN_CH8 = tuning("F3S_MIN_CH8", MIN_CH8_DEFAULT);
 constexpr int DIRECT_TILES_PER_WARP = 32;  // below this average load the schedule costs more than it saves
 constexpr int MAX_BUDGET_CH8 = 1 << 16;    // largest chunk (in 8-column tiles) a budgeted schedule may use
 
@@ -1022,6 +1029,10 @@ static void layout(Geometry &gm, long long total_t8, int heads, int d) {
 }
 
 // budget_bytes > 0: raise the split threshold (fewer, larger chunks) until the scratch fits.
+// Canonical schedule (f3s_set_canonical_chunk_tiles): 0 = off.
+static int g_canonical_ch8 = 0;
+extern "C" void f3s_set_canonical_chunk_tiles(int32_t tiles) { g_canonical_ch8 = tiles > 0 ? tiles : 0; }
+
 // phased: geometry of one launch of a two-phase call -- always scheduled (never the one-launch mode), never
 // the TMA path, and room in the unit list for the TC block per window that both launches work on.
 static Geometry geometry(int n_rw, long long n_tcb, int block_w, int heads, int d, size_t budget_bytes = 0,
@@ -1034,17 +1045,20 @@ static Geometry geometry(int n_rw, long long n_tcb, int block_w, int heads, int 
   if (phased && gm.kc.path == PATH_TMA) gm.kc.path = PATH_SPLIT;
   const long long total_t8 = (n_tcb + (phased ? n_rw : 0)) * (block_w / 8);
   const long long total_warps = (long long)sm_count() * gm.kc.warps;
-  gm.direct = (!phased && total_t8 * heads <= total_warps * DIRECT_TILES_PER_WARP) ? 1 : 0;
+  const bool canonical = g_canonical_ch8 > 0;
+  gm.direct = (!phased && !canonical && total_t8 * heads <= total_warps * DIRECT_TILES_PER_WARP) ? 1 : 0;
   // Many short windows (fewer than four 32-column steps on average, e.g. batches of small graphs):
   // the split-ring kernel's longer prologue costs more than its overlap gains (measured 0.31 vs
   // 0.21 ms on the molecule-batch workload), so the plain two-stage kernel is used there.
-  if (gm.kc.path == PATH_SPLIT && !gm.direct && total_t8 < 16ll * n_rw) gm.kc.path = PATH_CPASYNC;
+  if (gm.kc.path == PATH_SPLIT && !gm.direct && !canonical && total_t8 < 16ll * n_rw) gm.kc.path = PATH_CPASYNC;
   long long ch = (total_t8 * heads) / (total_warps * UNITS_PER_WARP);
+  if (canonical) ch = g_canonical_ch8;  // the same cut points whatever the load, the head count or the device
   ch = (ch + gm.kc.nt8 - 1) / gm.kc.nt8 * gm.kc.nt8;
-  if (ch < MIN_CH8) ch = MIN_CH8;
+  if (ch < MIN_CH8 && !canonical) ch = MIN_CH8;
   if (ch > (1 << 28)) ch = 1 << 28;
   gm.ch8 = (int)ch;
   layout(gm, total_t8, heads, d);
+  if (canonical) return gm;  // no growing of chunks to fit a budget: the call is refused if the scratch is too small
   // With a budget the chunks may grow, but only up to MAX_BUDGET_CH8 tiles: beyond that a single
   // warp would walk hundreds of thousands of columns on its own and the call is refused instead.
   while (budget_bytes > 0 && gm.total_bytes > budget_bytes && gm.ch8 * 2 <= MAX_BUDGET_CH8) {
@@ -1202,6 +1216,17 @@ struct FwdExtra {
 };
 enum { MODE_FULL = 0, MODE_PLAN_ONLY = 1, MODE_PLANNED = 2 };
 
+// Co-scheduling aid: the persistent kernels normally take one CTA on every SM, which leaves a collective
+// that is launched beside them (NCCL's kernels need SMs of their own) waiting until they finish.  A cap
+// below the SM count keeps that many SMs free.  0 = no cap.  Process-wide; the environment variable
+// F3S_MAX_CTAS gives the initial value.
+static int g_max_ctas = [] {
+  const char *e = getenv("F3S_MAX_CTAS");
+  const int v = e ? atoi(e) : 0;
+  return v > 0 ? v : 0;
+}();
+extern "C" void f3s_set_max_ctas(int32_t max_ctas) { g_max_ctas = max_ctas > 0 ? max_ctas : 0; }
+
 // Validation + launch shared by the entry points.  budget_bytes > 0 lets the schedule use
 // fewer, larger chunks so that its scratch fits in that many bytes.
 static int forward_impl(const int32_t *row_window_offset, const int32_t *sorted_row_windows,
@@ -1286,6 +1311,7 @@ static int forward_impl(const int32_t *row_window_offset, const int32_t *sorted_
   p.sm_trace = reinterpret_cast<unsigned long long *>(sm_trace);
 
   int grid = sm_count();
+  if (g_max_ctas > 0 && grid > g_max_ctas) grid = g_max_ctas;
   if (gm.direct) {  // one launch; no more CTAs than there are (head, window) pairs
     const long long units = (long long)n_row_windows * heads;
     if (units < grid) grid = (int)(units > 0 ? units : 1);

@@ -167,17 +167,25 @@ class ShardedAttention:
     row stride, so the interleaving costs nothing), which makes the exchange one collective instead of
     two.  ``send_buffers`` hands out the views a producer writes its K / V rows into.
 
-    With a ``local_last`` shard and more than one rank, ``forward`` overlaps the all-gather with compute:
-    the collective runs on a side stream while the first kernel launch works on the columns the rank
+    With ``two_phase=True``, a ``local_last`` shard and more than one rank, ``forward`` overlaps the
+    all-gather with compute: the collective runs on a side stream while the first kernel launch works on the columns the rank
     already holds (its own rows); the second launch waits for the collective's event and does the rest.
     No kernel reads another GPU's memory and nothing spins on a flag: two launches and one event.
 
     ``forward_fn(tcb, num_rows, q_local, k_full, v_full, scale_divisor) -> out_local`` replaces the CUDA
     path in the CPU tests, so that the partition / gather logic can run under gloo without a GPU."""
 
-    def __init__(self, shard: RowShard, device, block_w: int = 16, forward_fn=None, preprocess_fn=None, tcb=None):
+    def __init__(self, shard: RowShard, device, block_w: int = 16, forward_fn=None, preprocess_fn=None, tcb=None,
+                 two_phase: bool = False, reserve_sms: int = 16):
+        """``two_phase``: overlap the all-gather with a first kernel launch on the rank's own columns (needs
+        a ``local_last`` shard).  Off by default: on B200 / NVLink 5 the collective is short (about 0.1 ms for
+        60 MB) and cutting every window's work in two launches costs more than the overlap returns; it
+        pays when the exchange is long compared with the kernel.
+        ``reserve_sms``: SMs the two-phase forward leaves free for the collective's own kernels (the
+        fused kernel is persistent and would otherwise hold every SM until its launch is finished)."""
         import torch
 
+        self.reserve_sms = int(reserve_sms)
         self.shard = shard
         self.device = torch.device(device)
         self.block_w = block_w
@@ -195,7 +203,7 @@ class ShardedAttention:
         self._plan = None
         self._phased = None
         self._comm_stream = None
-        self.two_phase = bool(shard.local_last and shard.world > 1 and forward_fn is None)
+        self.two_phase = bool(two_phase and shard.local_last and shard.world > 1 and forward_fn is None)
 
     # views of the interleaved buffers
     @property
@@ -277,7 +285,12 @@ class ShardedAttention:
             self._all_gather()
             arrived = torch.cuda.Event()
             arrived.record(self._comm_stream)
+        if self.reserve_sms > 0:   # room for the collective's kernels beside the persistent fused kernel
+            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+            cabi.lib().f3s_set_max_ctas(max(1, sms - self.reserve_sms))
         p.launch_phase(1)          # columns this rank owns: reads only the send block
+        if self.reserve_sms > 0:
+            cabi.lib().f3s_set_max_ctas(0)
         cur.wait_event(arrived)
         p.launch_phase(2)          # everybody else's columns, continuing from phase 1's state
         # the next step's K / V may overwrite the send block only after the collective has read it; the
@@ -398,10 +411,17 @@ class HeadShardedPipeline:
     they are strided-batched outputs).  The reference is single-GPU; no counterpart there."""
 
     def __init__(self, rowptr: np.ndarray, colidx: np.ndarray, num_nodes: int, heads: int, rank: int, world: int,
-                 device, chunks: int = 4, block_w: int = 16, forward_fn=None):
+                 device, chunks: int = 4, block_w: int = 16, forward_fn=None, reserve_sms: int = 32, group=None):
+        """``reserve_sms``: SMs left to the collectives' kernels while the fused kernels run (the fused kernel
+        is persistent and would otherwise hold every SM until its launch is finished); ``group``: the process
+        group of the all-to-alls -- one whose NCCL communicator is capped at about as many CTAs as SMs are
+        reserved (``ProcessGroupNCCL.Options().config.max_ctas``) overlaps best (measured on 8 B200:
+        1.83 ms per step with 32 / 32 against 2.12 ms with neither)."""
         import torch
 
         assert heads % world == 0, "head sharding needs heads divisible by the number of ranks"
+        self.reserve_sms = int(reserve_sms)
+        self.group = group
         self.n, self.heads, self.rank, self.world = num_nodes, heads, rank, world
         self.hl = heads // world
         self.device = torch.device(device)
@@ -536,21 +556,24 @@ class HeadShardedPipeline:
 
         b = self._buffers(q_x)
         if self.device.type != "cuda":  # CPU tests: same data movement, no streams
-            _all_to_all(b["kv"], kv_x)
+            _all_to_all(b["kv"], kv_x, self.group)
             for c in range(self.chunks):
-                _all_to_all(b["q"][c], q_x[c])
+                _all_to_all(b["q"][c], q_x[c], self.group)
                 self._kernel(c, scale_divisor)
-                _all_to_all(b["out"][c], b["out_send"][c])
+                _all_to_all(b["out"][c], b["out_send"][c], self.group)
             return b["out"]
         if self._comm is None:
             self._comm = torch.cuda.Stream(device=self.device)
         cur, comm = torch.cuda.current_stream(self.device), self._comm
         comm.wait_stream(cur)  # inputs written, previous call's kernels done with the buffers
+        if self.reserve_sms > 0 and self.world > 1:
+            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+            cabi.lib().f3s_set_max_ctas(max(1, sms - self.reserve_sms))
         q_ready = []
         with torch.cuda.stream(comm):
-            _all_to_all(b["kv"], kv_x)
+            _all_to_all(b["kv"], kv_x, self.group)
             for c in range(self.chunks):
-                _all_to_all(b["q"][c], q_x[c])
+                _all_to_all(b["q"][c], q_x[c], self.group)
                 ev = torch.cuda.Event()
                 ev.record(comm)
                 q_ready.append(ev)
@@ -561,7 +584,8 @@ class HeadShardedPipeline:
             done.record(cur)
             with torch.cuda.stream(comm):
                 comm.wait_event(done)
-                _all_to_all(b["out"][c], b["out_send"][c])
+                _all_to_all(b["out"][c], b["out_send"][c], self.group)
+        cabi.lib().f3s_set_max_ctas(0)
         cur.wait_stream(comm)
         return b["out"]
 

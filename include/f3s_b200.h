@@ -143,6 +143,20 @@ int f3s_forward(const int32_t *row_window_offset, const int32_t *sorted_row_wind
                 size_t workspace_bytes, f3s_stream_t stream);
 
 /*
+ * The score stage alone on the 5th-generation tensor cores (tcgen05.mma, accumulator in tensor memory):
+ * sddmm_out receives what f3s_forward's sddmm_out receives -- the masked, unscaled scores of every 16x8
+ * tile, [n_tcb*block_w/8][16][8] fp32 -- i.e. the optional third output of the reference's f3s_1tb1tcb
+ * (saveSddmmResult, src/F3S_kernel.cu:99-115), computed as S^T = K_g Q^T with M = 128 gathered key rows,
+ * N = 16 query rows per product.  head_dim must be 64, one head; q rows at ld_q, k rows at ld_k elements.
+ * workspace: 64 bytes of device scratch (16-byte aligned) whose status word f3s_forward_status reads: a
+ * bounded wait that ran out is reported there.
+ */
+int f3s_sddmm_umma(const int32_t *row_window_offset, const int32_t *sparse_a_to_x_idx, const uint64_t *tcb_bitmap,
+                   int32_t num_nodes, int32_t n_row_windows, int64_t n_tcb, int32_t block_w, int32_t head_dim,
+                   int64_t ld_q, const void *q, int64_t ld_k, const void *k, float *sddmm_out, void *workspace,
+                   size_t workspace_bytes, f3s_stream_t stream);
+
+/*
  * f3s_forward writing an fp16 output ([num_nodes, heads*head_dim], 16-byte aligned) instead
  * of fp32: half the output bytes for callers whose next layer consumes fp16.  Accumulation
  * stays fp32; only the final store is rounded.  No reference counterpart (its ops always
@@ -225,6 +239,32 @@ int f3s_forward_phase(int32_t phase, const int32_t *row_window_offset, const int
                       int32_t heads, int32_t head_dim, int64_t ld_q, const void *q, int64_t ld_kv, const void *k,
                       const void *v, float scale_divisor, float *out, void *workspace, size_t workspace_bytes,
                       f3s_stream_t stream);
+
+/*
+ * Co-scheduling with a collective (no reference counterpart).  The fused kernels are persistent: one
+ * CTA per SM, each holding the SM's whole shared memory and register file until the call's work is
+ * done.  A collective launched beside them (NCCL's kernels need SMs of their own) would wait for that.
+ * f3s_set_max_ctas(n) makes every later forward launch of this process use at most n CTAs, leaving the
+ * other SMs to the collective; 0 removes the cap.  The environment variable F3S_MAX_CTAS sets the
+ * initial value.
+ */
+void f3s_set_max_ctas(int32_t max_ctas);
+
+/*
+ * Results that do not depend on how the work is divided (no reference counterpart).  By default the
+ * forward cuts heavy row windows into chunks whose size follows the load of the call (graph size, head
+ * count, SM count) and picks its kernel by the graph's shape; the partial results of the chunks are
+ * merged in a fixed order, so a call is deterministic, but two calls that see the same window inside
+ * different problems (one GPU vs. a row shard of it, one head vs. eight, workspace vs. built-in scratch)
+ * may round differently.  f3s_set_canonical_chunk_tiles(t) with t > 0 fixes the chunk size at t 8-column
+ * tiles (rounded up to a whole step of 4), always uses the scheduled kernels and one data path per head
+ * dimension: every window is then computed by the same sequence of operations in every such call and the
+ * outputs are equal bit for bit, provided the windows list their columns in the same order (row shards
+ * numbered in the padded gather layout that keeps the global order).  It costs a few per cent (more,
+ * smaller chunks on big graphs; no one-launch mode on small ones).  0 restores the default.  Process-wide.
+ * 128 is a sensible value.
+ */
+void f3s_set_canonical_chunk_tiles(int32_t tiles);
 
 /*
  * Device-side error reporting.  The reference's kernels report nothing and its host code ends the

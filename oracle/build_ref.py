@@ -30,7 +30,8 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
-REF = Path(os.environ.get("F3S_REFERENCE_DIR", "/root/reference")) / "src"
+# the reference checkout: F3S_REFERENCE_DIR, else a directory named "reference" beside this repository
+REF = Path(os.environ.get("F3S_REFERENCE_DIR", HERE.parent.parent / "reference")) / "src"
 NVCC = str(Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "bin" / "nvcc")
 REF_NVCC_FLAGS = ["-O3", "-use_fast_math", "-ftz=true", "-prec-div=false", "-prec-sqrt=false", "-lineinfo"]
 

@@ -27,7 +27,8 @@ import scipy.sparse  # noqa: F401  (the reference script uses ``scipy as sp`` th
 import torch
 
 HERE = Path(__file__).resolve().parent
-REF = Path(os.environ.get("F3S_REFERENCE_DIR", "/root/reference"))
+# the reference checkout: F3S_REFERENCE_DIR, else a directory named "reference" beside this repository
+REF = Path(os.environ.get("F3S_REFERENCE_DIR", HERE.parent.parent.parent / "reference"))
 
 
 def load_reference_script():
