@@ -60,6 +60,9 @@ def parse_args():
     ap.add_argument("--e2e-chunks", type=int, default=4, help="row chunks of the host-to-host pipeline")
     ap.add_argument("--head-chunks", type=int, default=4,
                     help="row chunks of the head-sharded pipeline (kernel of one chunk overlaps the exchange of others)")
+    ap.add_argument("--score-stage", action="store_true",
+                    help="1 GPU, one head: also time the score stage alone on tcgen05.mma / tensor memory "
+                         "(f3s_sddmm_umma) against the fused kernel with and without its score dump")
     ap.add_argument("--two-phase", action="store_true",
                     help="multi-GPU row sharding: overlap the all-gather with a first kernel launch on the rank's own "
                          "columns (default: collective, then one launch)")
@@ -818,6 +821,30 @@ def main():
                            note="pinned host Q/K/V in, pinned host output out; copies overlap the kernel; "
                                 "f3s_op_ms_per_step is the same transfer done around one F3S op call")
 
+    # ---- the score stage on the 5th-generation tensor cores, beside the fused kernel (optional)
+    score_stage = None
+    if args.score_stage and world == 1 and mode == "rows" and heads == 1 and d == 64:
+        dump = torch.empty(tcb["nTCB"] * 256, dtype=torch.float32, device=dev)
+        plan_dump = cabi.ForwardPlan(tcb, n, q_loc, k_loc, v_loc, SCALE_DIVISOR, sddmm_out=dump)
+        ws_u = torch.empty(64, dtype=torch.uint8, device=dev)
+
+        def umma_call():  # the C entry point itself: no status read-back inside the timed region
+            cabi.check(lib.f3s_sddmm_umma(tcb["rowWindowOffset"].data_ptr(), tcb["sparseAToXidx"].data_ptr(),
+                                          tcb["tcbBitMap"].data_ptr(), n, tcb["rowWindowOffset"].numel() - 1,
+                                          tcb["nTCB"], 16, d, d, q_loc.data_ptr(), d, k_loc.data_ptr(), dump.data_ptr(),
+                                          ws_u.data_ptr(), 64, torch.cuda.current_stream().cuda_stream))
+
+        for _ in range(3):
+            plan_dump.launch(), umma_call()
+        st = max(3, min(args.steps, 10))
+        (ms_d, _), (ms_u, _) = bench.timed(plan_dump.launch, st), bench.timed(umma_call, st)
+        cabi.check(lib.f3s_forward_status(ws_u.data_ptr(), None, torch.cuda.current_stream().cuda_stream))
+        score_stage = {"fused_kernel_ms": float(ms_steps.mean()), "fused_kernel_with_score_dump_ms": float(ms_d.mean()),
+                       "score_stage_tcgen05_ms": float(ms_u.mean()), "score_dump_bytes": int(dump.numel() * 4),
+                       "note": "f3s_sddmm_umma computes only S = Q K^T (masked) and writes the dump; the fused kernel "
+                               "with dump computes softmax and P V as well"}
+        del dump, plan_dump
+
     # ---- training path (optional): forward that also returns the row log-sum-exp, then dQ/dK/dV
     training = None
     if args.backward and world == 1 and mode == "rows":
@@ -922,6 +949,8 @@ def main():
         line["other_workloads"] = others
     if training is not None:
         line["training"] = training
+    if score_stage is not None:
+        line["score_stage"] = score_stage
     if world == 1 and not args.no_ref_cuda and ref_args is not None:
         line["reference_cuda_rebuilt"] = time_rebuilt_reference(*ref_args)
     if not args.no_cpu_baseline:

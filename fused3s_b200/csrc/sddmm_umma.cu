@@ -4,15 +4,18 @@
 // A row window has 16 query rows, below the smallest M (64) a tcgen05.mma accepts, so the product is
 // taken in its transposed form: S^T = K_g Q^T with M = 128 gathered key rows, N = 16 query rows,
 // K = 64 features.  One CTA of four warps owns one row window at a time:
-//   * every thread gathers one key row (128 bytes, eight 16-byte cp.async) of the step into a tile in the
+//   * every thread holds the id of one key row of the step; eight lanes copy a row together (one 128-byte
+//     request, 16-byte cp.async each) into a tile in the
 //     canonical K-major layout with 128-byte swizzle (row pitch 128 B, groups of eight rows 1024 B apart);
-//     two tiles alternate, so the gather of step i+1 is in flight while step i is multiplied and stored;
+//     three tiles rotate, so two gathers are in flight while a step is multiplied;
 //   * one thread issues four tcgen05.mma (K = 16 each; A = key tile, B = Q window, both read from shared
 //     memory through matrix descriptors) into a 128-lane x 16-column fp32 accumulator in TMEM and commits
-//     them to an mbarrier;
+//     them to an mbarrier; two accumulators alternate, so the product of step i runs while step i-1 is
+//     read back and stored;
 //   * every warp reads its 32 lanes of the accumulator with tcgen05.ld (thread = gathered column, 16
-//     registers = the 16 query rows), masks by the TC-block occupancy words and stores the scores in the
-//     layout of the reference's score dump (src/F3S_kernel.cu:99-115).
+//     registers = the 16 query rows), masks by the TC-block occupancy words, transposes through a small
+//     staging area and stores the scores with 16-byte coalesced writes in the layout of the reference's
+//     score dump (src/F3S_kernel.cu:99-115).
 // Every wait is bounded; a wait that runs out sets the status word and the CTA leaves after freeing its TMEM.
 //
 // This is the stage a tensor-memory version of the fused kernel would start from; it exists as an entry
@@ -28,8 +31,11 @@ constexpr int D = 64;
 constexpr int STEP_COLS = 128;                 // gathered key rows per product (M)
 constexpr int TILE_BYTES = STEP_COLS * D * 2;  // 16 KB
 constexpr int Q_BYTES = 16 * D * 2;            // 2 KB
-constexpr int SMEM_BYTES = 2 * TILE_BYTES + Q_BYTES + 1024;  // + alignment slack
-constexpr int TMEM_COLS = 32;                  // smallest allocation; 16 are used
+constexpr int STAGES = 3;                      // key tiles in flight
+constexpr int OUT_STRIDE = 17;                 // floats per staged column (16 rows + 1: conflict-free transposition)
+constexpr int OUT_BYTES = 4 * 32 * OUT_STRIDE * 4;  // per warp 32 columns x 16 rows, staged for coalesced stores
+constexpr int SMEM_BYTES = STAGES * TILE_BYTES + Q_BYTES + OUT_BYTES + 1024;  // + alignment slack
+constexpr int TMEM_COLS = 32;                  // smallest allocation: two accumulators of 16 columns
 constexpr int WAIT_LIMIT = 1 << 22;
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
@@ -102,16 +108,19 @@ struct Params {
 
 static __global__ void __launch_bounds__(THREADS) sddmm_umma_kernel(const Params p) {
   extern __shared__ unsigned char smem_raw[];
-  __shared__ __align__(8) unsigned long long mbar_storage;
+  __shared__ __align__(8) unsigned long long mbar_storage[2];
   __shared__ uint32_t tmem_base_s;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5;
   const uint32_t base_s = (smem_u32(smem_raw) + 1023u) & ~1023u;  // tiles sit on 1024-byte boundaries
-  const uint32_t k_s[2] = {base_s, base_s + (uint32_t)TILE_BYTES};
-  const uint32_t q_s = base_s + 2 * TILE_BYTES;
-  const uint32_t bar = smem_u32(&mbar_storage);
+  const uint32_t q_s = base_s + STAGES * TILE_BYTES;
+  float *stage = reinterpret_cast<float *>(smem_raw + (base_s - smem_u32(smem_raw)) + STAGES * TILE_BYTES + Q_BYTES) +
+                 warp * 32 * OUT_STRIDE;
+  const int lane = tid & 31;
+  const uint32_t bar0 = smem_u32(&mbar_storage[0]);
 
   if (tid == 0) {
-    mbar_init(bar, 1);
+    mbar_init(bar0, 1);
+    mbar_init(bar0 + 8, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {  // one warp allocates the CTA's tensor memory and gives up the right to allocate more
@@ -123,27 +132,83 @@ static __global__ void __launch_bounds__(THREADS) sddmm_umma_kernel(const Params
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_d = tmem_base_s;
-  const uint32_t my_taddr = tmem_d + ((uint32_t)(warp * 32) << 16);  // this warp's 32 lanes, column 0
-  uint32_t parity = 0;
+  const uint32_t tmem_d = tmem_base_s;  // two accumulators: columns [0,16) and [16,32)
+  const uint32_t my_lanes = (uint32_t)(warp * 32) << 16;
   bool ok = true;
-
-  // this thread's share of a gather: key row `tid` of the step, eight 16-byte pieces, swizzled
-  const uint32_t row_off = (uint32_t)tid * 128u;
-  const uint32_t sw = (uint32_t)(tid & 7);
+  // g counts the products this CTA has issued: key tile g % STAGES, accumulator and barrier g & 1, and the
+  // barrier's phase (g >> 1) & 1 follow from it, across row windows
+  uint32_t g = 0;
 
   for (int w = blockIdx.x; w < p.n_rw && ok; w += gridDim.x) {
     const int t8b = p.rwo[w] * p.t8_per_tcb, t8e = p.rwo[w + 1] * p.t8_per_tcb;
     const int nsteps = (t8e - t8b + 15) / 16;  // 16 tiles of 8 columns per product
     if (nsteps == 0) continue;
-    auto gather = [&](int step) {
-      const long long slot = (long long)(t8b + step * 16) * 8 + tid;
-      const bool real = slot < (long long)t8e * 8;
-      const int col = real ? __ldg(p.atox + slot) : 0;
-      const char *src = reinterpret_cast<const char *>(p.k + (size_t)col * p.ld_k);
-      const uint32_t dst = k_s[step & 1] + row_off;
+    const uint32_t g0 = g;  // product number of this window's step 0
+    const long long slots_end = (long long)t8e * 8;
+    // column id of this thread's key row, loaded one gather ahead of its use
+    long long next_slot = (long long)t8b * 8 + tid;
+    int next_col = next_slot < slots_end ? __ldg(p.atox + next_slot) : 0;
+    auto gather = [&](int step) {  // steps are gathered in order: 0, 1, 2, ...
+      const bool real = next_slot < slots_end;
+      const int col = next_col;
+      next_slot += STEP_COLS;
+      next_col = next_slot < slots_end ? __ldg(p.atox + next_slot) : 0;
+      // Eight consecutive lanes copy one key row (one 128-byte request), a warp the 32 rows whose ids its
+      // lanes hold: lane l copies piece l % 8 of rows l / 8 + 4 i, i = 0..7, of the warp's quarter of the tile.
+      const uint32_t tile = base_s + ((g0 + (uint32_t)step) % STAGES) * TILE_BYTES;
+      const int piece = lane & 7;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) cp_async16(dst + (((uint32_t)c ^ sw) << 4), src + c * 16, real ? 16 : 0);
+      for (int i = 0; i < 8; ++i) {
+        const int rl = (lane >> 3) + 4 * i;
+        const int idx = __shfl_sync(FULL, col, rl);
+        const int ok_row = __shfl_sync(FULL, (int)real, rl);
+        const int r = warp * 32 + rl;
+        cp_async16(tile + (uint32_t)r * 128u + (((uint32_t)piece ^ (uint32_t)(r & 7)) << 4),
+                   reinterpret_cast<const char *>(p.k + (size_t)idx * p.ld_k) + piece * 16, ok_row ? 16 : 0);
+      }
+    };
+    // Wait for the product of `step`, read this warp's 32 lanes of its accumulator, mask, store.
+    auto finish = [&](int step) {
+      const uint32_t gs = g0 + (uint32_t)step;
+      const int t8 = t8b + step * 16 + (tid >> 3);
+      unsigned long long w0 = 0, w1 = 0;
+      if (t8 < t8e) {  // occupancy words of this thread's 8-column tile, fetched while the product runs
+        w0 = __ldg(p.bitmap + (size_t)t8 * 2);
+        w1 = __ldg(p.bitmap + (size_t)t8 * 2 + 1);
+      }
+      bool mine = mbar_wait_bounded(bar0 + (gs & 1u) * 8, (gs >> 1) & 1u);
+      if (!mine) atomicExch(p.status, STATUS_WAIT_TIMEOUT);
+      if (!__syncthreads_and(mine)) {  // some thread gave up: everybody leaves
+        ok = false;
+        return;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      uint32_t acc[16];
+      tmem_ld16(tmem_d + my_lanes + (gs & 1u) * 16u, acc);
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");  // ordered before the next barrier
+      {  // mask (row i of the window, column c of the tile: bit 63 - (i % 8) * 8 - c of word i / 8) and stage
+        const int c = tid & 7;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const unsigned long long word = i < 8 ? w0 : w1;
+          const bool set = (word >> (63 - (i & 7) * 8 - c)) & 1ull;
+          stage[lane * OUT_STRIDE + i] = set ? __uint_as_float(acc[i]) : 0.f;
+        }
+      }
+      __syncwarp();
+      // the warp's four tiles are 2 KB of consecutive floats in the dump ([tile][row][column]): lane l
+      // writes floats 4 l .. 4 l + 3 of every tile = row l / 2, columns 4 (l % 2) .. + 3
+      const int t8w = t8b + step * 16 + warp * 4;  // first tile of this warp
+      const int row = lane >> 1, c0 = (lane & 1) * 4;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (t8w + k < t8e) {
+          const float *src = stage + (k * 8 + c0) * OUT_STRIDE + row;
+          const float4 v = make_float4(src[0], src[OUT_STRIDE], src[2 * OUT_STRIDE], src[3 * OUT_STRIDE]);
+          __stcs(reinterpret_cast<float4 *>(p.sddmm + (size_t)(t8w + k) * 128 + lane * 4), v);
+        }
+      }
+      __syncwarp();  // the staging area is rewritten by the next step
     };
     {  // Q window (rows past the last node read as zero) joins the first copy group
       const int r = tid >> 3, c = tid & 7;
@@ -153,55 +218,31 @@ static __global__ void __launch_bounds__(THREADS) sddmm_umma_kernel(const Params
     }
     gather(0);
     cp_async_commit();
-    for (int step = 0; step < nsteps; ++step) {
-      if (step + 1 < nsteps) gather(step + 1);
-      cp_async_commit();
-      cp_async_wait<1>();  // this step's tile (and Q) have landed for this thread
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // make them visible to the tensor core's reads
+    if (nsteps > 1) gather(1);
+    cp_async_commit();
+    for (int step = 0; step < nsteps && ok; ++step) {
+      cp_async_wait<1>();  // every group but the newest has landed: this step's tile (and Q) are there
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // visible to the tensor core's reads
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncthreads();
+      __syncthreads();  // also: every warp has read the accumulator this product is about to overwrite
       if (tid == 0) {
+        const uint32_t gs = g0 + (uint32_t)step;
+        const uint32_t tile = base_s + (gs % STAGES) * TILE_BYTES;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks)
-          mma_f16_ss(tmem_d, smem_desc(k_s[step & 1], ks * 32), smem_desc(q_s, ks * 32), ks > 0 ? 1u : 0u);
-        mma_commit(bar);
+          mma_f16_ss(tmem_d + (gs & 1u) * 16u, smem_desc(tile, ks * 32), smem_desc(q_s, ks * 32), ks > 0 ? 1u : 0u);
+        mma_commit(bar0 + (gs & 1u) * 8);
       }
-      // occupancy words of this thread's 8-column tile, fetched while the product runs
-      const int t8 = t8b + step * 16 + (tid >> 3);
-      unsigned long long w0 = 0, w1 = 0;
-      if (t8 < t8e) {
-        w0 = __ldg(p.bitmap + (size_t)t8 * 2);
-        w1 = __ldg(p.bitmap + (size_t)t8 * 2 + 1);
-      }
-      if (!mbar_wait_bounded(bar, parity)) {
-        atomicExch(p.status, STATUS_WAIT_TIMEOUT);
-        ok = false;
-      }
-      parity ^= 1u;
-      if (!__syncthreads_and(ok)) {  // some thread gave up: everybody leaves (the copies in flight are drained below)
-        ok = false;
-        break;
-      }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      uint32_t acc[16];
-      tmem_ld16(my_taddr, acc);
-      if (t8 < t8e) {  // row i of the window, column c of the tile: bit 63 - (i % 8) * 8 - c of word i / 8
-        const int c = tid & 7;
-        float *dst = p.sddmm + (size_t)t8 * 128 + c;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const unsigned long long word = i < 8 ? w0 : w1;
-          const bool set = (word >> (63 - (i & 7) * 8 - c)) & 1ull;
-          dst[i * 8] = set ? __uint_as_float(acc[i]) : 0.f;
-        }
-      }
-      // the accumulator is overwritten by the next product only after every warp has read it
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncthreads();
+      if (step > 0) finish(step - 1);  // runs beside the product just issued
+      // the tile of step-1 has been multiplied (its product was waited for): it takes the gather of step+2
+      if (ok && step + 2 < nsteps) gather(step + 2);
+      cp_async_commit();
     }
+    if (ok) finish(nsteps - 1);
+    g = g0 + (uint32_t)nsteps;
     cp_async_wait<0>();
-    __syncthreads();  // the Q tile and both key tiles are free for the next window
+    __syncthreads();  // the Q tile is free for the next window
   }
   cp_async_wait<0>();
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -249,7 +290,7 @@ extern "C" int f3s_sddmm_umma(const int32_t *row_window_offset, const int32_t *s
   F3S_CUDA_TRY(cudaMemsetAsync(workspace, 0, 64, stream));
   F3S_CUDA_TRY(cudaFuncSetAttribute(umma::sddmm_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     umma::SMEM_BYTES));
-  const long long want = (long long)sm_count() * 4;  // four CTAs per SM: 35 KB of shared memory, 32 TMEM columns each
+  const long long want = (long long)sm_count() * 3;  // three CTAs per SM: 61 KB of shared memory, 32 TMEM columns each
   const int grid = (int)(n_row_windows < want ? n_row_windows : want);
   umma::sddmm_umma_kernel<<<grid, umma::THREADS, umma::SMEM_BYTES, stream>>>(p);
   F3S_CHECK_LAUNCH();

@@ -33,11 +33,12 @@ def _i32(t, dev):
     return torch.as_tensor(t).to(device=dev, dtype=torch.int32)
 
 
-def concat_plans(plans: list[dict], num_nodes: list[int]):
+def concat_plans(plans: list[dict], num_nodes: list[int], validate: bool = False):
     """Batch plan of graphs 0..G-1 (dicts as returned by ``cabi.preprocess``, same ``block_w``,
     same device).  Returns (plan, node_offsets int64[G+1], total_nodes): graph g owns rows
     ``node_offsets[g] : node_offsets[g] + num_nodes[g]`` of the batch; ``total_nodes`` is the row
-    count the batch's Q/K/V need (the last graph is not padded)."""
+    count the batch's Q/K/V need (the last graph is not padded).  ``validate=True`` checks the assembled
+    plan with ``f3s_validate_plan`` (one pass over its index arrays, blocking) -- for parts of unknown origin."""
     if not plans:
         raise ValueError("empty batch")
     bw = plans[0]["block_w"]
@@ -89,6 +90,10 @@ def concat_plans(plans: list[dict], num_nodes: list[int]):
         out["edgeToColumn"] = torch.cat([p["edgeToColumn"] for p in plans])
     if all("edgeToRow" in p for p in plans):
         out["edgeToRow"] = torch.cat([p["edgeToRow"] for p in plans]) + per(row_base, n_edge)
+    if validate and dev.type == "cuda":
+        from . import cabi
+
+        cabi.validate_plan(out, total_nodes)
     return out, node_off, total_nodes
 
 

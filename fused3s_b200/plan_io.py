@@ -80,8 +80,10 @@ def load_plan(path) -> dict:
     return plan
 
 
-def to_device(plan: dict, device) -> dict:
-    """numpy plan -> dict of torch tensors in the form ``cabi.forward`` / ``cabi.ForwardPlan`` take."""
+def to_device(plan: dict, device, validate: bool = True) -> dict:
+    """numpy plan -> dict of torch tensors in the form ``cabi.forward`` / ``cabi.ForwardPlan`` take.
+    On a CUDA device the plan is checked once with ``f3s_validate_plan`` (every offset and column id the
+    kernels will dereference, against the ``num_cols`` the file records): a file is not a trusted source."""
     import torch
 
     out = dict(plan)
@@ -89,6 +91,10 @@ def to_device(plan: dict, device) -> dict:
         a = plan[k]
         t = torch.from_numpy(a.view(np.int64) if k == "tcbBitMap" else a).to(device)
         out[k] = t.view(torch.uint64) if k == "tcbBitMap" else t
+    if validate and torch.device(device).type == "cuda":
+        from . import cabi
+
+        cabi.validate_plan(out, int(plan.get("num_cols", plan.get("num_nodes", 0))))
     return out
 
 
