@@ -66,6 +66,8 @@ def parse_args():
     ap.add_argument("--two-phase", action="store_true",
                     help="multi-GPU row sharding: overlap the all-gather with a first kernel launch on the rank's own "
                          "columns (default: collective, then one launch)")
+    ap.add_argument("--kv-capped", action="store_true",
+                    help="head pipeline: run the K+V all-to-all on the capped communicator too (default: uncapped)")
     ap.add_argument("--reserve-sms", type=int, default=32,
                     help="multi-GPU, overlapped schemes (head pipeline, --two-phase): SMs the fused kernel leaves to the "
                          "collectives' kernels while both run")
@@ -524,7 +526,8 @@ def multi_gpu_heads_subrecord(bench, cfg, args, steps, rank, world, group=None):
     if heads % world != 0:
         return {"unavailable": f"{heads} heads do not divide over {world} GPUs"}
     attn = sharding.HeadShardedPipeline(g.rowptr, g.colidx, n, heads, rank, world, dev, chunks=args.head_chunks,
-                                        reserve_sms=args.reserve_sms, group=group)
+                                        reserve_sms=args.reserve_sms, group=group,
+                                        kv_group=group if args.kv_capped else None)
     rb, re_ = attn.row_begin, attn.row_end
     q_x = attn.to_exchange_layout(q_h[rb:re_].to(dev))
     kv_x = attn.kv_to_exchange_layout(k_h[rb:re_].to(dev), v_h[rb:re_].to(dev))
@@ -703,7 +706,8 @@ def main():
         rp_t = torch.from_numpy(g.rowptr).to(dev)
         ci_t = torch.from_numpy(g.colidx).to(dev)
         hp = sharding.HeadShardedPipeline(g.rowptr, g.colidx, n, heads, rank, world, dev, chunks=args.head_chunks,
-                                          reserve_sms=args.reserve_sms, group=overlap_group)
+                                          reserve_sms=args.reserve_sms, group=overlap_group,
+                                          kv_group=overlap_group if args.kv_capped else None)
         preprocess_ms = hp.preprocess_ms
         n_tcb_local = hp.n_tcb
         sum_u_local = distinct_window_columns(rp_t, ci_t, n)

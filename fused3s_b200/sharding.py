@@ -411,17 +411,21 @@ class HeadShardedPipeline:
     they are strided-batched outputs).  The reference is single-GPU; no counterpart there."""
 
     def __init__(self, rowptr: np.ndarray, colidx: np.ndarray, num_nodes: int, heads: int, rank: int, world: int,
-                 device, chunks: int = 4, block_w: int = 16, forward_fn=None, reserve_sms: int = 32, group=None):
+                 device, chunks: int = 4, block_w: int = 16, forward_fn=None, reserve_sms: int = 32, group=None,
+                 kv_group=None):
         """``reserve_sms``: SMs left to the collectives' kernels while the fused kernels run (the fused kernel
         is persistent and would otherwise hold every SM until its launch is finished); ``group``: the process
-        group of the all-to-alls -- one whose NCCL communicator is capped at about as many CTAs as SMs are
-        reserved (``ProcessGroupNCCL.Options().config.max_ctas``) overlaps best (measured on 8 B200:
+        group of the all-to-alls that run beside the kernels (Q and output pieces) -- one whose NCCL
+        communicator is capped at about as many CTAs as SMs are reserved; ``kv_group``: the group of the K+V
+        all-to-all, which precedes every kernel of the call and so may be the default, uncapped one (``ProcessGroupNCCL.Options().config.max_ctas``) overlaps best (measured on 8 B200:
         1.83 ms per step with 32 / 32 against 2.12 ms with neither)."""
         import torch
 
         assert heads % world == 0, "head sharding needs heads divisible by the number of ranks"
         self.reserve_sms = int(reserve_sms)
         self.group = group
+        # the K+V exchange runs before any kernel of the call, so it may use an uncapped communicator
+        self.kv_group = kv_group
         self.n, self.heads, self.rank, self.world = num_nodes, heads, rank, world
         self.hl = heads // world
         self.device = torch.device(device)
@@ -556,7 +560,7 @@ class HeadShardedPipeline:
 
         b = self._buffers(q_x)
         if self.device.type != "cuda":  # CPU tests: same data movement, no streams
-            _all_to_all(b["kv"], kv_x, self.group)
+            _all_to_all(b["kv"], kv_x, self.kv_group)
             for c in range(self.chunks):
                 _all_to_all(b["q"][c], q_x[c], self.group)
                 self._kernel(c, scale_divisor)
@@ -571,7 +575,7 @@ class HeadShardedPipeline:
             cabi.lib().f3s_set_max_ctas(max(1, sms - self.reserve_sms))
         q_ready = []
         with torch.cuda.stream(comm):
-            _all_to_all(b["kv"], kv_x, self.group)
+            _all_to_all(b["kv"], kv_x, self.kv_group)
             for c in range(self.chunks):
                 _all_to_all(b["q"][c], q_x[c], self.group)
                 ev = torch.cuda.Event()

@@ -82,3 +82,34 @@ def test_f3s_extension_module_surface():
         F3S.preprocess_gpu(torch.zeros(1, dtype=torch.int32), torch.zeros(2, dtype=torch.int32), 1, 16, 16,
                            torch.zeros(1, dtype=torch.int32), torch.zeros(1, dtype=torch.int32),
                            torch.zeros(1, dtype=torch.int32))
+
+
+def test_newer_entry_points_reject_bad_arguments_before_any_cuda_call():
+    from fused3s_b200 import cabi
+
+    lib = cabi.lib()
+    # two-launch forward: head_dim 64 only, phase 1 or 2
+    assert lib.f3s_forward_phased_workspace_bytes(10, 100, 16, 1, 32) == 0
+    assert lib.f3s_forward_phased_workspace_bytes(10, 100, 16, 2, 64) > lib.f3s_forward_workspace_bytes(10, 100, 16, 2, 64)
+    rc = lib.f3s_forward_phase(3, None, None, None, None, None, 0, 16, 1, 0, 16, 1, 64, 64, None, 64, None, None, 8.0,
+                               None, None, 0, None)
+    assert rc == cabi.ERR_INVALID_ARG and b"phase" in lib.f3s_last_error_string()
+    rc = lib.f3s_forward_phase(1, None, None, None, None, None, 0, 16, 1, 0, 16, 1, 32, 32, None, 32, None, None, 8.0,
+                               None, None, 0, None)
+    assert rc == cabi.ERR_UNSUPPORTED
+    # score stage on tcgen05: head_dim 64 only
+    rc = lib.f3s_sddmm_umma(None, None, None, 16, 1, 0, 16, 32, 32, None, 32, None, None, None, 0, None)
+    assert rc == cabi.ERR_UNSUPPORTED and b"64" in lib.f3s_last_error_string()
+    # plan validation needs its 16 bytes of scratch and real arrays
+    rc = lib.f3s_validate_plan(None, None, None, 1, 0, 16, 16, None, 0, None)
+    assert rc == cabi.ERR_INVALID_ARG
+    # status decoding is pure host code
+    assert lib.f3s_status_word_to_code(0) == cabi.OK
+    assert lib.f3s_status_word_to_code(1) == cabi.ERR_DEVICE and b"overflow" in lib.f3s_last_error_string()
+    assert lib.f3s_status_word_to_code(2) == cabi.ERR_DEVICE and b"wait" in lib.f3s_last_error_string()
+    rc = lib.f3s_forward_status(None, None, None)
+    assert rc == cabi.ERR_INVALID_ARG
+    assert lib.f3s_kernel_launch_count() >= 0
+    lib.f3s_set_max_ctas(0)
+    lib.f3s_set_canonical_chunk_tiles(0)
+    lib.f3s_debug_set_unit_list_limit(0)
