@@ -63,6 +63,9 @@ def parse_args():
     ap.add_argument("--score-stage", action="store_true",
                     help="1 GPU, one head: also time the score stage alone on tcgen05.mma / tensor memory "
                          "(f3s_sddmm_umma) against the fused kernel with and without its score dump")
+    ap.add_argument("--collective", default="auto", choices=["auto", "nccl", "multimem"],
+                    help="multi-GPU row sharding: the K/V all-gather through NCCL or through NVSwitch multicast "
+                         "(torch symmetric memory); auto = multicast when it can be set up, else NCCL")
     ap.add_argument("--two-phase", action="store_true",
                     help="multi-GPU row sharding: overlap the all-gather with a first kernel launch on the rank's own "
                          "columns (default: collective, then one launch)")
@@ -176,7 +179,9 @@ def sharding_note(args, heads):
     if mode == "auto" or heads % args.gpus != 0:
         mode = "heads" if (args.sharding == "auto" and heads > 1 and heads % args.gpus == 0) else "rows"
     if mode == "rows":
-        return ("row windows by TC-block count; K and V all-gathered by one NCCL collective inside every step" +
+        return ("row windows by TC-block count; K and V all-gathered by one collective inside every step "
+                f"(--collective {args.collective}: NVSwitch multicast through torch symmetric memory when available, "
+                "else NCCL)" +
                 (", overlapped with a first kernel launch on the rank's own columns" if args.two_phase else
                  ", then one kernel launch"))
     if mode == "heads-resident":
@@ -585,11 +590,16 @@ def main():
     dev = torch.device("cuda", local_rank)
     overlap_group = None
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # a rank that never joins ends the others' collectives with an error after this long (torch's NCCL
+        # watchdog), instead of leaving them waiting for ever
+        import datetime
+
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
         if args.nccl_max_ctas > 0:  # collectives that share the GPU with the fused kernel: a narrow communicator
             opts = dist.ProcessGroupNCCL.Options()
             opts.config.max_ctas = args.nccl_max_ctas
-            overlap_group = dist.new_group(ranks=list(range(world)), backend="nccl", pg_options=opts)
+            overlap_group = dist.new_group(ranks=list(range(world)), backend="nccl", pg_options=opts,
+                                           timeout=datetime.timedelta(seconds=300))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     bench = Bench(dev, world)
     lib = cabi.lib()
@@ -626,7 +636,7 @@ def main():
         weights = None
         if world > 1:  # TC blocks per window of the whole graph: what the partition is balanced by
             weights = cabi.window_tcb_counts(ci_full, rp_full, n).cpu().numpy()
-        shard = sharding.make_shard(g.rowptr, g.colidx, n, rank, world, window_weight=weights, local_last=world > 1)
+        shard = sharding.make_shard(g.rowptr, g.colidx, n, rank, world, window_weight=weights, local_last=world > 1 and args.two_phase)
         del rp_full, ci_full
         rp_t = torch.from_numpy(shard.rowptr).to(dev)
         ci_t = torch.from_numpy(shard.padded_colidx()).to(dev)
@@ -647,7 +657,8 @@ def main():
         k_pin = k_h[r0:r1].contiguous().pin_memory()
         v_pin = v_h[r0:r1].contiguous().pin_memory()
         q_loc = q_pin.to(dev)
-        attn = sharding.ShardedAttention(shard, dev, 16, tcb=tcb, two_phase=args.two_phase, reserve_sms=args.reserve_sms)
+        attn = sharding.ShardedAttention(shard, dev, 16, tcb=tcb, two_phase=args.two_phase, reserve_sms=args.reserve_sms,
+                                         collective=args.collective)
         if world > 1:  # the local K/V rows live in the send block of the all-gather
             k_loc, v_loc = attn.send_buffers(q_loc)
             k_loc[: r1 - r0].copy_(k_pin)
@@ -770,7 +781,7 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
     if world > 1 and mode == "rows":  # the parts of the step, each timed alone
         ms_ag, _ = bench.timed(attn._all_gather, args.steps)
-        parts = {"all_gather_alone_ms": float(ms_ag.mean())}
+        parts = {"all_gather_alone_ms": float(ms_ag.mean()), "collective": attn.collective_used}
         if attn._phased is not None:
             ph = attn._phased
             ms_2p, _ = bench.timed(lambda: (ph.launch_phase(1), ph.launch_phase(2)), args.steps)

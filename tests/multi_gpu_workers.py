@@ -25,7 +25,9 @@ def setup():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev)
+    import datetime
+
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=240))
     return rank, world, dev
 
 
@@ -45,14 +47,17 @@ def check_rows_against_oracle(g, q, k, v, out, a, b, scale, seed):
 
 def rows():
     rank, world, dev = setup()
+    used = []
     for cfg, sc in ((4, 0.05), (5, 0.02)):
         g = graphs.make_config(cfg, scale=sc)
         n = g.num_nodes
         q, k, v = graphs.make_features(g)
         rp, ci = torch.from_numpy(g.rowptr).to(dev), torch.from_numpy(g.colidx).to(dev)
         w = cabi.window_tcb_counts(ci, rp, n).cpu().numpy()
-        shard = sharding.make_shard(g.rowptr, g.colidx, n, rank, world, window_weight=w, local_last=True)
-        att = sharding.ShardedAttention(shard, dev, two_phase=(cfg == 4))  # both forms of the forward
+        # cfg4: own columns numbered last, all-gather overlapped with a first launch (NCCL);
+        # cfg5: order-preserving numbering, one collective (NVSwitch multicast when it can be set up) + one launch
+        shard = sharding.make_shard(g.rowptr, g.colidx, n, rank, world, window_weight=w, local_last=(cfg == 4))
+        att = sharding.ShardedAttention(shard, dev, two_phase=(cfg == 4))
         assert att.two_phase == (cfg == 4)
         a, b = shard.row_begin, shard.row_end
         ql = q[a:b].to(dev)
@@ -72,8 +77,9 @@ def rows():
         dist.all_gather(parts, t)
         parts = [float(x) for x in parts]
         assert max(parts) <= 1.05 * (sum(parts) / world) + 64, parts
+        used.append(att.collective_used)
     if rank == 0:
-        print(f"row-sharded two-phase forward ok on {world} GPUs")
+        print(f"row-sharded forward (collectives: {used}) ok on {world} GPUs")
     dist.destroy_process_group()
 
 
