@@ -180,8 +180,8 @@ def sharding_note(args, heads):
         mode = "heads" if (args.sharding == "auto" and heads > 1 and heads % args.gpus == 0) else "rows"
     if mode == "rows":
         return ("row windows by TC-block count; K and V all-gathered by one collective inside every step "
-                f"(--collective {args.collective}: NVSwitch multicast through torch symmetric memory when available, "
-                "else NCCL)" +
+                f"(--collective {args.collective}: auto = NVSwitch multicast through torch symmetric memory from 8 ranks "
+                "on when available, else NCCL)" +
                 (", overlapped with a first kernel launch on the rank's own columns" if args.two_phase else
                  ", then one kernel launch"))
     if mode == "heads-resident":

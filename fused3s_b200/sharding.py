@@ -186,8 +186,9 @@ class ShardedAttention:
         ``collective``: "nccl" = ``all_gather_into_tensor``; "multimem" = torch symmetric memory's one-shot
         all-gather through NVSwitch multicast (``symm_mem.multimem_all_gather_out``: every rank stores its
         block once to the multicast address; measured 0.102 ms against 0.140 ms for 60 MB on 8 B200);
-        "auto" = multimem when the buffers can be set up on this machine, else NCCL.  ``collective_used``
-        says which one runs."""
+        every rank's egress is one block, so it wins when the blocks are small -- at 2 GPUs (30 MB blocks) it
+        measured 0.133 ms against NCCL's 0.095 ms); "auto" = multimem from 8 ranks on when the buffers can be
+        set up on this machine, else NCCL.  ``collective_used`` says which one runs."""
         import torch
 
         self.reserve_sms = int(reserve_sms)
@@ -250,7 +251,8 @@ class ShardedAttention:
             self._mm_group = None
             self.collective_used = "nccl"
             want_mm = (self.collective != "nccl" and s.world > 1 and like.device.type == "cuda"
-                       and not s.local_last and self.forward_fn is None)
+                       and not s.local_last and self.forward_fn is None
+                       and (self.collective == "multimem" or s.world >= 8))
             if want_mm:
                 try:
                     self._send, self._kv, self._mm_group = self._symmetric_buffers(tail, like.dtype, like.device)

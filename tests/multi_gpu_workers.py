@@ -57,7 +57,7 @@ def rows():
         # cfg4: own columns numbered last, all-gather overlapped with a first launch (NCCL);
         # cfg5: order-preserving numbering, one collective (NVSwitch multicast when it can be set up) + one launch
         shard = sharding.make_shard(g.rowptr, g.colidx, n, rank, world, window_weight=w, local_last=(cfg == 4))
-        att = sharding.ShardedAttention(shard, dev, two_phase=(cfg == 4))
+        att = sharding.ShardedAttention(shard, dev, two_phase=(cfg == 4), collective="nccl" if cfg == 4 else "multimem")
         assert att.two_phase == (cfg == 4)
         a, b = shard.row_begin, shard.row_end
         ql = q[a:b].to(dev)
