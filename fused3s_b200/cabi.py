@@ -122,7 +122,7 @@ def lib() -> C.CDLL:
         l.f3s_sddmm_umma.argtypes = [vp, vp, vp, i32, i32, i64, i32, i32, i64, vp, i64, vp, vp, vp, sz, vp]
         l.f3s_set_canonical_chunk_tiles.restype = None
         l.f3s_set_canonical_chunk_tiles.argtypes = [i32]
-        l.f3s_set_max_ctas.restype = None
+        l.f3s_set_max_ctas.restype = C.c_int32
         l.f3s_set_max_ctas.argtypes = [i32]
         l.f3s_forward_status.restype = C.c_int
         l.f3s_forward_status.argtypes = [vp, vp, vp]

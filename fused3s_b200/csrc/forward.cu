@@ -1218,7 +1218,11 @@ static int g_max_ctas = [] {
   const int v = e ? atoi(e) : 0;
   return v > 0 ? v : 0;
 }();
-extern "C" void f3s_set_max_ctas(int32_t max_ctas) { g_max_ctas = max_ctas > 0 ? max_ctas : 0; }
+extern "C" int32_t f3s_set_max_ctas(int32_t max_ctas) {
+  const int previous = g_max_ctas;
+  g_max_ctas = max_ctas > 0 ? max_ctas : 0;
+  return previous;
+}
 
 // Validation + launch shared by the entry points.  budget_bytes > 0 lets the schedule use
 // fewer, larger chunks so that its scratch fits in that many bytes.

@@ -330,12 +330,15 @@ class ShardedAttention:
             self._all_gather()
             arrived = torch.cuda.Event()
             arrived.record(self._comm_stream)
+        previous = None
         if self.reserve_sms > 0:   # room for the collective's kernels beside the persistent fused kernel
             sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-            cabi.lib().f3s_set_max_ctas(max(1, sms - self.reserve_sms))
-        p.launch_phase(1)          # columns this rank owns: reads only the send block
-        if self.reserve_sms > 0:
-            cabi.lib().f3s_set_max_ctas(0)
+            previous = cabi.lib().f3s_set_max_ctas(max(1, sms - self.reserve_sms))
+        try:
+            p.launch_phase(1)      # columns this rank owns: reads only the send block
+        finally:
+            if previous is not None:
+                cabi.lib().f3s_set_max_ctas(previous)
         cur.wait_event(arrived)
         p.launch_phase(2)          # everybody else's columns, continuing from phase 1's state
         # the next step's K / V may overwrite the send block only after the collective has read it; the
@@ -615,9 +618,22 @@ class HeadShardedPipeline:
             self._comm = torch.cuda.Stream(device=self.device)
         cur, comm = torch.cuda.current_stream(self.device), self._comm
         comm.wait_stream(cur)  # inputs written, previous call's kernels done with the buffers
+        previous = None
         if self.reserve_sms > 0 and self.world > 1:
             sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-            cabi.lib().f3s_set_max_ctas(max(1, sms - self.reserve_sms))
+            previous = cabi.lib().f3s_set_max_ctas(max(1, sms - self.reserve_sms))
+        try:
+            self._enqueue(b, q_x, kv_x, scale_divisor, cur, comm)
+        finally:
+            if previous is not None:
+                cabi.lib().f3s_set_max_ctas(previous)
+        cur.wait_stream(comm)
+        return b["out"]
+
+    def _enqueue(self, b, q_x, kv_x, scale_divisor, cur, comm):
+        """The collectives and kernels of one call, in issue order (see the class docstring)."""
+        import torch
+
         q_ready = []
         with torch.cuda.stream(comm):
             _all_to_all(b["kv"], kv_x, self.kv_group)
@@ -634,9 +650,6 @@ class HeadShardedPipeline:
             with torch.cuda.stream(comm):
                 comm.wait_event(done)
                 _all_to_all(b["out"][c], b["out_send"][c], self.group)
-        cabi.lib().f3s_set_max_ctas(0)
-        cur.wait_stream(comm)
-        return b["out"]
 
 
 # ---------------------------------------------------------------------------------------------------

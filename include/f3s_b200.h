@@ -245,10 +245,10 @@ int f3s_forward_phase(int32_t phase, const int32_t *row_window_offset, const int
  * CTA per SM, each holding the SM's whole shared memory and register file until the call's work is
  * done.  A collective launched beside them (NCCL's kernels need SMs of their own) would wait for that.
  * f3s_set_max_ctas(n) makes every later forward launch of this process use at most n CTAs, leaving the
- * other SMs to the collective; 0 removes the cap.  The environment variable F3S_MAX_CTAS sets the
- * initial value.
+ * other SMs to the collective; 0 removes the cap.  Returns the previous value, so that a caller can put it
+ * back.  The environment variable F3S_MAX_CTAS sets the initial value.
  */
-void f3s_set_max_ctas(int32_t max_ctas);
+int32_t f3s_set_max_ctas(int32_t max_ctas);
 
 /*
  * Results that do not depend on how the work is divided (no reference counterpart).  By default the
