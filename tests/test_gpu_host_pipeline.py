@@ -10,14 +10,17 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
+@pytest.mark.parametrize("kv_halves", [False, True])
 @pytest.mark.parametrize("cfg,scale,chunks", [(4, 0.02, 4), (5, 0.01, 3), (1, 1.0, 8)])
-def test_host_pipeline_matches_single_call(cfg, scale, chunks):
+def test_host_pipeline_matches_single_call(cfg, scale, chunks, kv_halves):
     from fused3s_b200 import cabi
     from fused3s_b200.host_pipeline import HostPipelinedAttention
 
     g = graphs.make_config(cfg, scale=scale)
     q, k, v = (x.pin_memory() for x in graphs.make_features(g))
-    pipe = HostPipelinedAttention(g.rowptr, g.colidx, g.num_nodes, g.heads, g.dim, DEV, chunks=chunks)
+    pipe = HostPipelinedAttention(g.rowptr, g.colidx, g.num_nodes, g.heads, g.dim, DEV, chunks=chunks,
+                                  kv_halves=kv_halves)
+    assert pipe.kv_halves == kv_halves  # K and V in two halves, every chunk as the two-launch forward
     out_host = torch.empty(q.shape, dtype=torch.float32).pin_memory()
     for _ in range(2):  # buffers and plans are reused from the second call on
         out_host.fill_(float("nan"))
