@@ -237,6 +237,18 @@ class ShardedAttention:
         full = symm.empty((s.gathered_rows, 2) + tail, dtype=dtype, device=device)
         symm.rendezvous(send, gname)
         symm.rendezvous(full, gname)
+        # trust but verify, once: every rank's block must arrive where the kernel will look for it
+        import torch
+
+        full.zero_()
+        send.fill_(float(s.rank + 1))
+        torch.ops.symm_mem.multimem_all_gather_out(send, gname, full)
+        torch.cuda.synchronize(device)
+        firsts = full.view(s.world, -1)[:, 0].float().cpu()
+        lasts = full.view(s.world, -1)[:, -1].float().cpu()
+        want = torch.arange(1, s.world + 1, dtype=torch.float32)
+        if not (torch.equal(firsts, want) and torch.equal(lasts, want)):
+            raise RuntimeError("the multicast all-gather did not deliver every rank's block")
         send.zero_()
         full.zero_()
         return send, full, gname
