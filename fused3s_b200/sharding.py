@@ -266,13 +266,21 @@ class ShardedAttention:
                        and not s.local_last and self.forward_fn is None
                        and (self.collective == "multimem" or s.world >= 8))
             if want_mm:
+                import torch.distributed as dist
+
+                err, bufs = None, None
                 try:
-                    self._send, self._kv, self._mm_group = self._symmetric_buffers(tail, like.dtype, like.device)
+                    bufs = self._symmetric_buffers(tail, like.dtype, like.device)
+                except Exception as e:  # not available here: every rank has to learn of it
+                    err = e
+                agreed = torch.tensor([0 if bufs is None else 1], device=like.device)
+                dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+                if int(agreed) == 1:
+                    self._send, self._kv, self._mm_group = bufs
                     self.collective_used = "multimem"
                     return
-                except Exception:
-                    if self.collective == "multimem":
-                        raise
+                if self.collective == "multimem":
+                    raise err if err is not None else RuntimeError("another rank could not set up the multicast all-gather")
             self._kv = torch.zeros((s.padded_cols, 2) + tail, dtype=like.dtype, device=like.device)
             if s.local_last and s.world > 1:  # the own block follows the gathered ones and is the send buffer
                 self._send = self._kv[s.gathered_rows:]
