@@ -185,3 +185,29 @@ def test_two_rank_sharded_forward_equals_single(tmp_path, heads):
     mp.spawn(_worker, args=(2, _free_port(), rowptr, colidx, n, heads, out_file), nprocs=2, join=True)
     res = torch.load(out_file)
     assert res["ok"] and res["rows"][0] == 0 and res["rows"][-1] == n
+
+
+def test_phase_split_array_names_the_only_block_with_columns_of_both_kinds():
+    """The two-launch forward's ``phase_split[w]``: first TC block of window w whose FIRST column id is at or
+    above the split; every block before the one preceding it holds only lower ids, every block from it on only
+    higher ones (checked by brute force on the oracle's TC-block arrays, CPU tensors)."""
+    from fused3s_b200 import cabi
+    from oracle import preprocess_oracle as po
+
+    n = 400
+    rowptr, colidx = random_csr(n, 30, 21)
+    tcb_np = po.preprocess(colidx, rowptr, n, 16, 16)
+    tcb = {"block_w": 16, "rowWindowOffset": torch.from_numpy(tcb_np["rowWindowOffset"]),
+           "sparseAToXidx": torch.from_numpy(tcb_np["sparseAToXidx"])}
+    rwo, atox = tcb_np["rowWindowOffset"], tcb_np["sparseAToXidx"].reshape(-1, 16)
+    for split in (0, 1, 137, 250, n, n + 5):
+        ps = cabi.phase_split_array(tcb, split).numpy()
+        for w in range(len(rwo) - 1):
+            a, z, lb = int(rwo[w]), int(rwo[w + 1]), int(ps[w])
+            assert a <= lb <= z
+            for t in range(a, z):
+                first = int(atox[t, 0])
+                assert (first >= split) == (t >= lb), (w, t, first, split, lb)
+            # blocks before lb - 1 hold nothing at or above the split (padding slots of a last block are 0)
+            for t in range(a, max(a, lb - 1)):
+                assert int(atox[t].max()) < split
