@@ -116,6 +116,9 @@ class ClockSampler:
                  str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            t0 = time.perf_counter()  # nvidia-smi needs a moment to attach: wait for its first sample
+            while not self.rows and time.perf_counter() - t0 < 5.0:
+                time.sleep(0.05)
         except Exception:
             self.proc = None
 
@@ -775,6 +778,16 @@ def main():
         if done % 8 == 0:
             torch.cuda.synchronize()
     torch.cuda.synchronize()
+    if world > 1 and args.min_warmup_seconds > 0:
+        # several ranks: the number of further warm-up steps that fills the same time is agreed on first
+        spent = torch.tensor([(time.perf_counter() - t_warm) / max(1, done)], device=dev, dtype=torch.float64)
+        dist.all_reduce(spent, op=dist.ReduceOp.MAX)
+        extra = int(min(20000, max(0.0, args.min_warmup_seconds - float(spent) * done) / max(1e-6, float(spent))))
+        for i in range(extra):
+            step_device()
+            if i % 64 == 63:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
     launches0 = lib.f3s_kernel_launch_count()
     ms_steps, _ = bench.timed(step_device, args.steps)
     gpu_launches = int(lib.f3s_kernel_launch_count() - launches0)  # counted by the library, this rank
