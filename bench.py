@@ -343,7 +343,7 @@ def roofline_record(b_alg, b_min, kern_ms, peak, peak_src, traffic, kv_bytes, l2
                     hbm_gather_gbs=None):
     """The HBM fraction the contract asks for, plus the two measured ceilings that actually bind a gather
     kernel: this package's probe kernel gathers 128-byte rows at random ids from a table of the size of
-    K + V (L2-resident case) and from a 4 GiB table (HBM case).  ``frac_mixed`` compares the kernel time with
+    K + V (L2-resident case) and from a 2 GiB table (HBM case).  ``frac_mixed`` compares the kernel time with
     gathered bytes / gather ceiling + streamed bytes (Q, output, metadata) / copy rate."""
     achieved = b_alg / (kern_ms * 1e-3) / 1e9
     rec = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -363,7 +363,7 @@ def roofline_record(b_alg, b_min, kern_ms, peak, peak_src, traffic, kv_bytes, l2
         rec["t_roof_mixed_ms"] = t_roof
         rec["frac_mixed"] = t_roof / kern_ms
     rec["gather_peak_source"] = ("f3s_probe_gather_rows (this package): 128-byte rows at seeded random ids, loads only, "
-                                 "best of 5, same process; table = size of K + V of one head (L2) / 4 GiB (HBM)")
+                                 "best of 5, same process; table = size of K + V of one head (L2) / 2 GiB (HBM)")
     rec["note"] = ("frac = algorithmic bytes / kernel time / measured HBM copy rate. K + V of a head fit the L2 cache, so "
                    "the gathers never reach DRAM and frac may exceed 1; frac_l2 and frac_mixed (against the measured L2 "
                    "gather rate) say how far the kernel is from the roof that binds" if l2_resident else
@@ -500,7 +500,7 @@ def single_gpu_subrecord(bench, cfg, args, steps):
     peak, peak_src = measured_peaks()
     kv_bytes = 2 * n * d * 2  # K + V of ONE head: heads are processed one after the other by every warp
     l2 = cabi.gather_rate_gbs(kv_bytes, dev) if kv_bytes < 100e6 else None
-    hbm_g = cabi.gather_rate_gbs(4 << 30, dev, n_ids=1 << 23)
+    hbm_g = cabi.gather_rate_gbs(2 << 30, dev, n_ids=1 << 23)
     t = float(ms.mean())
     rec = {"workload": workload_config(args, g)["workload"], "ms_per_step": t, "ms_per_step_median": float(np.median(ms)),
            "edge_gflops": 4.0 * d * heads * g.nnz / (t * 1e-3) / 1e9, "steps": steps, "gpu_launches": launches,
@@ -932,7 +932,7 @@ def main():
     # ---- the L2 ceiling for the gathers, measured here with this package's own probe kernel
     kv_bytes = 2 * n * d * 2  # K + V of one head (heads are walked one after the other)
     l2_gbs = cabi.gather_rate_gbs(kv_bytes, dev) if (rank == 0 and kv_bytes < 100e6) else None
-    hbm_gather_gbs = cabi.gather_rate_gbs(4 << 30, dev, n_ids=1 << 23) if rank == 0 else None
+    hbm_gather_gbs = cabi.gather_rate_gbs(2 << 30, dev, n_ids=1 << 23) if rank == 0 else None
 
     # ---- the other workloads (every rank takes part in the multi-GPU one)
     others = None
