@@ -492,6 +492,7 @@ window_fill_kernel(const int *__restrict__ colidx, const int *__restrict__ rowpt
                    unsigned long long *__restrict__ bitmap, int *scratch_a, int *scratch_b) {
   extern __shared__ int dsm[];
   __shared__ int s_aux[33];
+  __shared__ int s_rp[17];  // row pointers of the window: the row of an edge follows from its position
   int *s_hist = dsm, *s_cnt = s_hist + FILL_HIST_INTS;
   unsigned long long *s_bmp = reinterpret_cast<unsigned long long *>(s_cnt + NB_CAP);
   unsigned *s_bmp32 = reinterpret_cast<unsigned *>(s_bmp);
@@ -527,6 +528,7 @@ window_fill_kernel(const int *__restrict__ colidx, const int *__restrict__ rowpt
     if (one_pass) {
       const int nd = 1 << bits;
       for (int i = tid; i < FILL_WARPS * nd; i += FILL_THREADS) s_hist[i] = 0;
+      if (tid < 17) s_rp[tid] = rowptr[min(row0 + tid, n_nodes)];
       __syncthreads();
       // warp `warp` owns the contiguous slice [beg, end) of the window's edges (CSR order), lane l
       // of it the elements beg + 32 j + l: the order the stable scatter below relies on
@@ -542,18 +544,20 @@ window_fill_kernel(const int *__restrict__ colidx, const int *__restrict__ rowpt
           const int e = s + i;
           const int rank = e2c[e];
           const int tl = rank >> lbw, c = rank & (bw - 1);
-          const int r = e2r[e] & 15;
+          int r = 0;  // last row whose first edge is at or before e (empty rows share a pointer and are skipped)
+          if (s_rp[r + 8] <= e) r += 8;
+          if (s_rp[r + 4] <= e) r += 4;
+          if (s_rp[r + 2] <= e) r += 2;
+          if (s_rp[r + 1] <= e) r += 1;
           atox[(((size_t)tcb0 + tl) << lbw) + c] = colidx[e];
           const int sub = (c >> 3) * sub_per_col + (r >> 3);
           const int bitpos = 63 - ((r & 7) * 8 + (c & 7));
           atomicOr(&s_bmp32[((tl * wpt + sub) << 1) + (bitpos >> 5)], 1u << (bitpos & 31));
-          atomicAdd(&s_cnt[tl], 1);
-          atomicAdd(&myh[tl], 1);
+          atomicAdd(&myh[tl], 1);  // the per-TCB edge counts are the column sums of these histograms
           keys[j] = (tl << 8) | ((r << lbw) + c);
         }
       }
       __syncthreads();
-      for (int i = tid; i < nb; i += FILL_THREADS) tcb_off[1 + tcb0 + i] = s_cnt[i];
       for (int i = tid; i < nb * wpt; i += FILL_THREADS) bitmap[(size_t)tcb0 * wpt + i] = s_bmp[i];
       {  // TCB-major, warp-minor exclusive offsets of the per-warp histograms
         int carry = 0;
@@ -562,6 +566,7 @@ window_fill_kernel(const int *__restrict__ colidx, const int *__restrict__ rowpt
           int tot = 0;
           if (d < nd)
             for (int x = 0; x < FILL_WARPS; ++x) tot += s_hist[x * nd + d];
+          if (d < nb) tcb_off[1 + tcb0 + d] = tot;  // edges of TC block d (scanned into offsets afterwards)
           int total;
           int run = carry + block_excl_scan<FILL_WARPS>(tot, s_aux, total);
           if (d < nd)
