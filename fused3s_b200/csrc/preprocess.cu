@@ -32,7 +32,7 @@ constexpr int WIN_CAP = 4096;  // largest window (edges) sorted entirely in shar
 constexpr int SCHED_THREADS = 1024;
 constexpr int SCHED_WARPS = SCHED_THREADS / 32;
 
-enum { PH_ERROR = 0, PH_MAX_TCB = 1, PH_SUM_TCB = 2, PH_N_LARGE = 3, PH_N_LARGE_FILL = 4, PH_INTS = 16 };
+enum { PH_ERROR = 0, PH_MAX_TCB = 1, PH_SUM_TCB = 2, PH_N_LARGE = 3, PH_N_LARGE_FILL = 4, PH_FILL_NEXT = 5, PH_INTS = 16 };
 
 // ---- block-wide helpers ---------------------------------------------------------------
 
@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(WIN_THREADS)
 window_rank_kernel(const int *__restrict__ colidx, const int *__restrict__ rowptr, int n_nodes, int n_cols,
                    int bw, const int *__restrict__ large_list, int *__restrict__ block_partition,
                    int *__restrict__ e2c, int *__restrict__ e2r, int *scratch_a, int *scratch_b, int *hdr) {
-  extern __shared__ int dsm[];
+  extern __shared__ __align__(16) int dsm[];
   __shared__ int s_aux[33];
   __shared__ int s_min[WIN_WARPS], s_max[WIN_WARPS];
   const int tid = threadIdx.x;
@@ -479,20 +479,97 @@ constexpr int FILL_THREADS = 512;
 constexpr int FILL_WARPS = FILL_THREADS / 32;
 constexpr int FILL_DBITS = 10;  // NB_CAP TC blocks in one pass
 constexpr int FILL_KREG = 32;   // edges per thread on the one-pass path
+constexpr int FILL_AHEAD = 4;   // steps of the edge walk whose loads are in flight together
 constexpr int FILL_HIST_INTS = FILL_WARPS << FILL_DBITS;
 constexpr int FILL_SMEM_BYTES = (FILL_HIST_INTS + NB_CAP) * (int)sizeof(int) + NB_CAP * 4 * 8;
 static_assert((1 << FILL_DBITS) >= NB_CAP, "one radix pass must cover every TCB id of the one-pass path");
-static_assert(FILL_KREG * FILL_THREADS <= NB_CAP * 4 * 8, "the staged tile bytes reuse the occupancy words' memory");
+constexpr int FILL_STAGE_MAX = FILL_HIST_INTS * (int)sizeof(int) - 16;  // tile bytes of one window, staged with a skew
+static_assert(FILL_KREG * FILL_THREADS + 16 <= NB_CAP * 4 * 8, "the staged tile bytes (and their skew) reuse the occupancy words' memory");
 
-__global__ void __launch_bounds__(FILL_THREADS)
+// Row (0..15) of edge e inside a window whose 17 row pointers are rp: the last row that starts at or before e
+// (empty rows share a pointer with their successor and are skipped).
+__device__ __forceinline__ int row_of_edge(const int *rp, int e) {
+  int r = 0;
+  if (rp[r + 8] <= e) r += 8;
+  if (rp[r + 4] <= e) r += 4;
+  if (rp[r + 2] <= e) r += 2;
+  if (rp[r + 1] <= e) r += 1;
+  return r;
+}
+
+// What a CTA of window_fill_kernel needs to know about entry li of its window list (nothing is loaded past the list).
+struct FillWindow {
+  int w, s, n, tcb0, nb;
+};
+__device__ __forceinline__ FillWindow fill_window(int li, int n_large, const int *__restrict__ large_list,
+                                                  const int *__restrict__ rowptr, const int *__restrict__ rwo,
+                                                  int n_nodes) {
+  FillWindow f = {0, 0, 0, 0, 0};
+  if (li < n_large) {
+    f.w = large_list[li];
+    const int row0 = f.w * 16, row1 = min(row0 + 16, n_nodes);
+    f.s = rowptr[row0];
+    f.n = rowptr[row1] - f.s;
+    f.tcb0 = rwo[f.w];
+    f.nb = rwo[f.w + 1] - f.tcb0;
+  }
+  return f;
+}
+
+// Requests the 128-byte lines of a[0 .. n) into L2 (no data returned, nothing waits for it).
+__device__ __forceinline__ void prefetch_l2_lines(const int *a, int n, int tid, int n_threads) {
+  for (int i = tid * 32; i < n; i += n_threads * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(a + i));
+  if (tid == 0 && n > 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(a + n - 1));
+}
+
+// Tile ids (row * BW + column) of the occupied positions of one TC block in row-major order, from its
+// occupancy words: word (c / 8) * (BW / 8) + (r / 8) holds position (r, c) at bit 63 - ((r % 8) * 8 + c % 8),
+// i.e. byte 7 - r % 8 of a word is the 8-column strip of row r, column 0 in its top bit.  The strips are
+// regrouped into 32-bit words of consecutive positions (top bit first), so that the tile id of a set bit is
+// 32 * word + count of leading zeros.
+template <int BW>
+__device__ __forceinline__ unsigned char *tile_bytes_of_block(const unsigned long long (&wv)[4], unsigned char *out) {
+  constexpr int NW = 16 * BW / 32;
+  unsigned m[NW];
+  if (BW == 16) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {  // rows 8h .. 8h+7: left strips in wv[h], right strips in wv[2 + h]
+      const unsigned l_hi = (unsigned)(wv[h] >> 32), l_lo = (unsigned)wv[h];
+      const unsigned r_hi = (unsigned)(wv[2 + h] >> 32), r_lo = (unsigned)wv[2 + h];
+      m[4 * h + 0] = __byte_perm(l_hi, r_hi, 0x3726);  // rows 8h, 8h+1
+      m[4 * h + 1] = __byte_perm(l_hi, r_hi, 0x1504);  // rows 8h+2, 8h+3
+      m[4 * h + 2] = __byte_perm(l_lo, r_lo, 0x3726);
+      m[4 * h + 3] = __byte_perm(l_lo, r_lo, 0x1504);
+    }
+  } else {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {  // 8-wide blocks: a word already holds rows 8h .. 8h+7 in row-major order
+      m[2 * h + 0] = (unsigned)(wv[h] >> 32);
+      m[2 * h + 1] = (unsigned)wv[h];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < NW; ++k) {
+    unsigned x = m[k];
+    while (x) {
+      const int z = __clz(x);
+      *out++ = (unsigned char)(32 * k + z);
+      x &= ~(0x80000000u >> z);
+    }
+  }
+  return out;
+}
+
+__global__ void __launch_bounds__(FILL_THREADS, 2)  // two CTAs per SM: 64 registers, 100 KB of shared memory each
 window_fill_kernel(const int *__restrict__ colidx, const int *__restrict__ rowptr, int n_nodes, int n_rw, int bw,
                    const int *__restrict__ e2c, const int *__restrict__ e2r, const int *__restrict__ rwo,
-                   const int *__restrict__ large_list, const int *__restrict__ hdr, int *__restrict__ tcb_rowid,
+                   const int *__restrict__ large_list, int *hdr, int *__restrict__ tcb_rowid,
                    unsigned char *__restrict__ tile_id, int *__restrict__ tcb_off, int *__restrict__ atox,
                    unsigned long long *__restrict__ bitmap, int *scratch_a, int *scratch_b) {
-  extern __shared__ int dsm[];
+  extern __shared__ __align__(16) int dsm[];
   __shared__ int s_aux[33];
   __shared__ int s_rp[17];  // row pointers of the window: the row of an edge follows from its position
+  __shared__ int s_next;
   int *s_hist = dsm, *s_cnt = s_hist + FILL_HIST_INTS;
   unsigned long long *s_bmp = reinterpret_cast<unsigned long long *>(s_cnt + NB_CAP);
   unsigned *s_bmp32 = reinterpret_cast<unsigned *>(s_bmp);
@@ -501,20 +578,228 @@ window_fill_kernel(const int *__restrict__ colidx, const int *__restrict__ rowpt
   const int wpt = 16 * bw / 64;
   const int sub_per_col = bw / 8;
   const int lbw = (bw == 16) ? 4 : 3;
-  for (int li = blockIdx.x; li < n_large; li += gridDim.x) {
-    __syncthreads();  // the previous window's shared memory is no longer read
-    const int w = large_list[li];
-    const int row0 = w * 16, row1 = min(row0 + 16, n_nodes);
-    const int s = rowptr[row0], t = rowptr[row1];
-    const int n = t - s;
-    const int tcb0 = rwo[w], tcb1 = rwo[w + 1];
-    const int nb = tcb1 - tcb0;
+  const bool vec16 = ((reinterpret_cast<uintptr_t>(bitmap) | reinterpret_cast<uintptr_t>(atox)) & 15) == 0;
+  // A CTA pulls its windows from a counter (they differ in size by 10x) and always knows the next one: that
+  // window's header is loaded, and its slices of edgeToColumn and colIdx are requested into L2, while the
+  // current window is worked on -- the walk over a window's edges otherwise pays DRAM latency per step.
+  if (tid == 0) s_next = atomicAdd(&hdr[PH_FILL_NEXT], 1);
+  __syncthreads();
+  int li = s_next;
+  FillWindow ahead = fill_window(li, n_large, large_list, rowptr, rwo, n_nodes);
+  for (;;) {
+    __syncthreads();  // the previous window's shared memory (and s_next) is no longer read
+    if (li >= n_large) break;
+    if (tid == 0) s_next = atomicAdd(&hdr[PH_FILL_NEXT], 1);
+    __syncthreads();
+    const int w = ahead.w, s = ahead.s, n = ahead.n, tcb0 = ahead.tcb0, nb = ahead.nb;
+    const int row0 = w * 16, tcb1 = tcb0 + nb;
+    li = s_next;
+    ahead = fill_window(li, n_large, large_list, rowptr, rwo, n_nodes);  // used after the walk below
     if (nb <= 0) continue;
     const bool in_smem = nb <= NB_CAP;
-    const bool one_pass = in_smem && n <= FILL_KREG * FILL_THREADS;
     int bits = 0;
     while ((1 << bits) < nb) ++bits;
     for (int i = tid; i < nb; i += FILL_THREADS) tcb_rowid[tcb0 + i] = w;
+
+    if (n <= FILL_STAGE_MAX) {
+      // Common case.  The window's TC blocks are taken NB_CAP at a time (nearly always all at once); for every
+      // such range one walk over the window's edges builds the column list and the occupancy words in shared
+      // memory.  If every row's columns ascend strictly (checked in the first walk), the CSR order of the edges
+      // inside a TC block is the row-major order of its occupancy bits, so the tile ids and the per-block edge
+      // counts follow from the occupancy words alone: one thread per TC block, no second walk, no sort.
+      if (tid < 17) s_rp[tid] = rowptr[min(row0 + tid, n_nodes)];
+      int *s_atox = s_hist;  // at most NB_CAP * 16 = FILL_HIST_INTS column slots
+      bool slow = false;
+      int edges_done = 0;
+      const int per = ((n + FILL_WARPS - 1) / FILL_WARPS + 31) & ~31;
+      const int beg = min(n, warp * per), end = min(n, beg + per);
+      for (int tl0 = 0; tl0 < nb; tl0 += NB_CAP) {
+        const int nbc = min(NB_CAP, nb - tl0);
+        if (tl0 > 0) __syncthreads();  // the previous range's tile bytes have left
+        {
+          uint4 *z = reinterpret_cast<uint4 *>(s_bmp);  // an even number of 64-bit words per TC block
+          for (int i = tid; i < nbc * wpt / 2; i += FILL_THREADS) z[i] = make_uint4(0u, 0u, 0u, 0u);
+          // every column slot is written by at least one edge, but for the unused ones of the last block: they read 0
+          if (tl0 + nbc == nb && tid < bw) s_atox[(nbc - 1) * bw + tid] = 0;
+        }
+        __syncthreads();
+        // Warp `warp` walks the contiguous slice [beg, end) of the window's edges, 32 at a time: a lane's edges
+        // ascend, so its row only moves forward (rp_r, nxt: the pointers of its row and of the next one), and the
+        // edge before lane 0's is lane 31's of the previous step.
+        bool unsorted = false;
+        int r = 0, rp_r = s_rp[0], nxt = s_rp[1];
+        int prev_last = (beg > 0 && beg < end) ? e2c[s + beg - 1] : -1;
+        for (int i0 = beg; i0 < end; i0 += 32 * FILL_AHEAD) {  // warp-uniform bounds: the shuffles below are full-warp
+          int rk[FILL_AHEAD], cl[FILL_AHEAD];
+#pragma unroll
+          for (int u = 0; u < FILL_AHEAD; ++u) {  // all loads of FILL_AHEAD steps are in flight before the first use
+            const int e = s + min(i0 + 32 * u + lane, end - 1);
+            rk[u] = e2c[e];
+            cl[u] = colidx[e];
+          }
+#pragma unroll
+          for (int u = 0; u < FILL_AHEAD; ++u) {
+            if (i0 + 32 * u >= end) break;
+            const int i = i0 + 32 * u + lane;
+            const bool valid = i < end;
+            const int e = s + i;
+            const int rank = rk[u];
+            int prev = __shfl_up_sync(0xffffffffu, rank, 1);
+            if (lane == 0) prev = prev_last;
+            prev_last = __shfl_sync(0xffffffffu, rank, 31);
+            const int tl = (rank >> lbw) - tl0, c = rank & (bw - 1);
+            if (valid) {
+              while (nxt <= e) {  // s_rp[16] is the window's end: never reached
+                rp_r = nxt;
+                ++r;
+                nxt = s_rp[r + 1];
+              }
+              unsorted |= (e > rp_r) & (prev >= rank);
+              if ((unsigned)tl < (unsigned)nbc) {
+                s_atox[(tl << lbw) + c] = cl[u];
+                // 32-bit half and bit of position (r, c): word (c / 8) * (bw / 8) + r / 8, bit 63 - ((r % 8) * 8 + c % 8)
+                const int half = ((tl * wpt + (c >> 3) * sub_per_col + (r >> 3)) << 1) + 1 - ((r >> 2) & 1);
+                atomicOr(&s_bmp32[half], 0x80000000u >> (((r & 3) << 3) + (c & 7)));
+              }
+            }
+          }
+        }
+        if (tl0 == 0) {
+          slow = __syncthreads_or(unsorted);
+          prefetch_l2_lines(e2c + ahead.s, ahead.n, tid, FILL_THREADS);
+          prefetch_l2_lines(colidx + ahead.s, ahead.n, tid, FILL_THREADS);
+          if (slow && !(in_smem && n <= FILL_KREG * FILL_THREADS)) break;  // left to the general path
+        } else {
+          __syncthreads();
+        }
+        {  // both lists start on a 16-byte boundary in shared and in global memory and hold a multiple of 16 bytes
+          const size_t g0 = (size_t)tcb0 + tl0;
+          if (vec16) {
+            const uint4 *sb = reinterpret_cast<const uint4 *>(s_bmp), *sa = reinterpret_cast<const uint4 *>(s_atox);
+            uint4 *gb = reinterpret_cast<uint4 *>(bitmap + g0 * wpt);
+            uint4 *ga = reinterpret_cast<uint4 *>(atox + g0 * bw);
+            for (int i = tid; i < nbc * wpt / 2; i += FILL_THREADS) gb[i] = sb[i];
+            for (int i = tid; i < nbc * bw / 4; i += FILL_THREADS) ga[i] = sa[i];
+          } else {  // output arrays that do not start on a 16-byte boundary
+            for (int i = tid; i < nbc * wpt; i += FILL_THREADS) bitmap[g0 * wpt + i] = s_bmp[i];
+            for (int i = tid; i < nbc * bw; i += FILL_THREADS) atox[g0 * bw + i] = s_atox[i];
+          }
+        }
+        // The tile bytes are staged at the offset that gives them the alignment (mod 16) of their place in
+        // tcblocktile_id, so that all but the ragged ends leave as 16-byte stores.
+        unsigned char *gt = tile_id + s + edges_done;
+        const int skew = (int)(reinterpret_cast<uintptr_t>(gt) & 15);
+        unsigned char *stage;
+        int n_stage;
+
+        if (!slow) {
+          __syncthreads();  // the column list has left; its memory takes the staged tile bytes
+          stage = reinterpret_cast<unsigned char *>(s_hist) + skew;
+          int carry = 0;
+          for (int base = 0; base < nbc; base += FILL_THREADS) {
+            const int d = base + tid;
+            unsigned long long wv[4] = {0ull, 0ull, 0ull, 0ull};
+            int cnt = 0;
+            if (d < nbc) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                if (k < wpt) {
+                  wv[k] = s_bmp[d * wpt + k];
+                  cnt += __popcll(wv[k]);
+                }
+              tcb_off[1 + tcb0 + tl0 + d] = cnt;  // edges of the TC block (scanned into offsets afterwards)
+            }
+            int total;
+            const int off = carry + block_excl_scan<FILL_WARPS>(cnt, s_aux, total);
+            carry += total;
+            if (cnt > 0) {
+              if (bw == 16) tile_bytes_of_block<16>(wv, stage + off);
+              else tile_bytes_of_block<8>(wv, stage + off);
+            }
+          }
+          n_stage = carry;
+        } else {
+          // Unsorted rows or repeated edges, window small enough for registers: stable single-pass radix sort
+          // of the (TC block, tile id) words on the TC-block bits.  (Here the range is the whole window.)
+          const int nd = 1 << bits;
+          __syncthreads();  // the column list has left; its memory takes the histograms
+          for (int i = tid; i < FILL_WARPS * nd; i += FILL_THREADS) s_hist[i] = 0;
+          __syncthreads();
+          // the same slices as above (CSR order), lane l of a warp the elements beg + 32 j + l: the order the
+          // stable scatter below relies on
+          int *myh = s_hist + warp * nd;
+          int keys[FILL_KREG];
+#pragma unroll
+          for (int j = 0; j < FILL_KREG; ++j) {
+            const int i = beg + j * 32 + lane;
+            keys[j] = -1;
+            if (i < end) {
+              const int e = s + i;
+              const int rank = e2c[e];
+              const int tl = rank >> lbw, c = rank & (bw - 1);
+              const int r = row_of_edge(s_rp, e);
+              atomicAdd(&myh[tl], 1);  // the per-TCB edge counts are the column sums of these histograms
+              keys[j] = (tl << 8) | ((r << lbw) + c);
+            }
+          }
+          __syncthreads();
+          {  // TCB-major, warp-minor exclusive offsets of the per-warp histograms
+            int carry = 0;
+            for (int base = 0; base < nd; base += FILL_THREADS) {
+              const int d = base + tid;
+              int tot = 0;
+              if (d < nd)
+                for (int x = 0; x < FILL_WARPS; ++x) tot += s_hist[x * nd + d];
+              if (d < nb) tcb_off[1 + tcb0 + d] = tot;  // edges of TC block d (scanned into offsets afterwards)
+              int total;
+              int run = carry + block_excl_scan<FILL_WARPS>(tot, s_aux, total);
+              if (d < nd)
+                for (int x = 0; x < FILL_WARPS; ++x) {
+                  const int v = s_hist[x * nd + d];
+                  s_hist[x * nd + d] = run;
+                  run += v;
+                }
+              carry += total;
+            }
+          }
+          __syncthreads();  // offsets complete; the occupancy words have been stored, their memory is reused
+          stage = reinterpret_cast<unsigned char *>(s_bmp) + skew;
+#pragma unroll
+          for (int j = 0; j < FILL_KREG; ++j) {
+            if (beg + j * 32 >= end) break;  // warp-uniform
+            const int key = keys[j];
+            const bool valid = key >= 0;
+            const unsigned d = (unsigned)key >> 8;
+            const unsigned peers = same_digit_lanes(d, valid);
+            const int rank = __popc(peers & ((1u << lane) - 1u));
+            const int base = valid ? myh[d] : 0;
+            __syncwarp();
+            if (valid) {
+              stage[base + rank] = (unsigned char)(key & 255);
+              if (lane == __ffs(peers) - 1) myh[d] = base + __popc(peers);
+            }
+            __syncwarp();
+          }
+          n_stage = n;
+        }
+        __syncthreads();
+        {
+          const int head = min(n_stage, (16 - skew) & 15);  // bytes before the first 16-byte boundary of the output
+          const int n16 = (n_stage - head) >> 4;
+          if (tid < head) gt[tid] = stage[tid];
+          const uint4 *sv = reinterpret_cast<const uint4 *>(stage + head);
+          uint4 *gv = reinterpret_cast<uint4 *>(gt + head);
+          for (int i = tid; i < n16; i += FILL_THREADS) gv[i] = sv[i];
+          const int done = head + (n16 << 4);
+          if (tid < n_stage - done) gt[done + tid] = stage[done + tid];
+        }
+        edges_done += n_stage;
+      }
+      if (!slow || (in_smem && n <= FILL_KREG * FILL_THREADS)) continue;
+    }
+
+    // ---- general path: windows of more than FILL_STAGE_MAX edges, and unsorted ones too large for registers
+    __syncthreads();
     if (in_smem) {
       for (int i = tid; i < nb; i += FILL_THREADS) s_cnt[i] = 0;
       for (int i = tid; i < nb * wpt; i += FILL_THREADS) s_bmp[i] = 0ull;
@@ -524,84 +809,6 @@ window_fill_kernel(const int *__restrict__ colidx, const int *__restrict__ rowpt
     }
     // every TCB but the last is full; the last one's unused column slots read 0
     for (int i = tid; i < bw; i += FILL_THREADS) atox[(size_t)(tcb1 - 1) * bw + i] = 0;
-
-    if (one_pass) {
-      const int nd = 1 << bits;
-      for (int i = tid; i < FILL_WARPS * nd; i += FILL_THREADS) s_hist[i] = 0;
-      if (tid < 17) s_rp[tid] = rowptr[min(row0 + tid, n_nodes)];
-      __syncthreads();
-      // warp `warp` owns the contiguous slice [beg, end) of the window's edges (CSR order), lane l
-      // of it the elements beg + 32 j + l: the order the stable scatter below relies on
-      const int per = ((n + FILL_WARPS - 1) / FILL_WARPS + 31) & ~31;
-      const int beg = min(n, warp * per), end = min(n, beg + per);
-      int *myh = s_hist + warp * nd;
-      int keys[FILL_KREG];
-#pragma unroll
-      for (int j = 0; j < FILL_KREG; ++j) {
-        const int i = beg + j * 32 + lane;
-        keys[j] = -1;
-        if (i < end) {
-          const int e = s + i;
-          const int rank = e2c[e];
-          const int tl = rank >> lbw, c = rank & (bw - 1);
-          int r = 0;  // last row whose first edge is at or before e (empty rows share a pointer and are skipped)
-          if (s_rp[r + 8] <= e) r += 8;
-          if (s_rp[r + 4] <= e) r += 4;
-          if (s_rp[r + 2] <= e) r += 2;
-          if (s_rp[r + 1] <= e) r += 1;
-          atox[(((size_t)tcb0 + tl) << lbw) + c] = colidx[e];
-          const int sub = (c >> 3) * sub_per_col + (r >> 3);
-          const int bitpos = 63 - ((r & 7) * 8 + (c & 7));
-          atomicOr(&s_bmp32[((tl * wpt + sub) << 1) + (bitpos >> 5)], 1u << (bitpos & 31));
-          atomicAdd(&myh[tl], 1);  // the per-TCB edge counts are the column sums of these histograms
-          keys[j] = (tl << 8) | ((r << lbw) + c);
-        }
-      }
-      __syncthreads();
-      for (int i = tid; i < nb * wpt; i += FILL_THREADS) bitmap[(size_t)tcb0 * wpt + i] = s_bmp[i];
-      {  // TCB-major, warp-minor exclusive offsets of the per-warp histograms
-        int carry = 0;
-        for (int base = 0; base < nd; base += FILL_THREADS) {
-          const int d = base + tid;
-          int tot = 0;
-          if (d < nd)
-            for (int x = 0; x < FILL_WARPS; ++x) tot += s_hist[x * nd + d];
-          if (d < nb) tcb_off[1 + tcb0 + d] = tot;  // edges of TC block d (scanned into offsets afterwards)
-          int total;
-          int run = carry + block_excl_scan<FILL_WARPS>(tot, s_aux, total);
-          if (d < nd)
-            for (int x = 0; x < FILL_WARPS; ++x) {
-              const int v = s_hist[x * nd + d];
-              s_hist[x * nd + d] = run;
-              run += v;
-            }
-          carry += total;
-        }
-      }
-      __syncthreads();  // offsets complete; the occupancy words have been stored, their memory is reused
-      unsigned char *stage = reinterpret_cast<unsigned char *>(s_bmp);
-#pragma unroll
-      for (int j = 0; j < FILL_KREG; ++j) {
-        if (beg + j * 32 >= end) break;  // warp-uniform
-        const int key = keys[j];
-        const bool valid = key >= 0;
-        const unsigned d = (unsigned)key >> 8;
-        const unsigned peers = same_digit_lanes(d, valid);
-        const int rank = __popc(peers & ((1u << lane) - 1u));
-        const int base = valid ? myh[d] : 0;
-        __syncwarp();
-        if (valid) {
-          stage[base + rank] = (unsigned char)(key & 255);
-          if (lane == __ffs(peers) - 1) myh[d] = base + __popc(peers);
-        }
-        __syncwarp();
-      }
-      __syncthreads();
-      for (int i = tid; i < n; i += FILL_THREADS) tile_id[s + i] = stage[i];
-      continue;
-    }
-
-    // ---- general path
     __syncthreads();
     int *buf0 = scratch_a + s, *buf1 = scratch_b + s;
     for (int i = tid; i < n; i += FILL_THREADS) {
@@ -941,7 +1148,8 @@ extern "C" int f3s_preprocess_fill(const int32_t *colidx, const int32_t *rowptr,
               "null edge array");
   int *hdr = reinterpret_cast<int *>(ws + L.off_hdr);
   int *large_list = reinterpret_cast<int *>(ws + L.off_list);
-  F3S_CUDA_TRY(cudaMemsetAsync(hdr + PH_N_LARGE_FILL, 0, sizeof(int), stream));
+  static_assert(PH_FILL_NEXT == PH_N_LARGE_FILL + 1, "one memset clears both");
+  F3S_CUDA_TRY(cudaMemsetAsync(hdr + PH_N_LARGE_FILL, 0, 2 * sizeof(int), stream));
   window_fill_small<<<(n_rw + SW_WARPS - 1) / SW_WARPS, SW_WARPS * 32, 0, stream>>>(
       colidx, rowptr, num_nodes, n_rw, block_w, edge_to_column, edge_to_row, row_window_offset, tcblock_rowid,
       tcblocktile_id, tcblock_offset, sparse_a_to_x_idx, reinterpret_cast<unsigned long long *>(tcb_bitmap), hdr,

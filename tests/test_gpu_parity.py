@@ -72,12 +72,15 @@ def test_preprocess_configs_bit_exact(cfg, scale, bw):
     assert_tcb_equal(got, want, f"cfg{cfg} bw={bw}")
 
 
-def test_preprocess_window_larger_than_shared_memory():
-    # one window with far more than 4096 edges takes the global-scratch sort path
+@pytest.mark.parametrize("hub_degree", [3000, 4500])
+def test_preprocess_window_larger_than_shared_memory(hub_degree):
+    # one window with far more than 4096 edges takes the global-scratch sort path of phase 1; with 48 000 edges
+    # phase 2 still stages its tile bytes in shared memory (in several ranges of TC blocks), with 72 000 it
+    # takes the general path through the workspace
     n = 6000
     rng = np.random.default_rng(3)
     deg = np.full(n, 3, np.int64)
-    deg[32:48] = 3000
+    deg[32:48] = hub_degree
     cols = [np.sort(rng.choice(n, size=d, replace=False)) for d in deg]
     rowptr = np.zeros(n + 1, np.int32)
     rowptr[1:] = np.cumsum(deg)
@@ -85,6 +88,35 @@ def test_preprocess_window_larger_than_shared_memory():
     want = po.preprocess(colidx, rowptr, n, 16, 16)
     got = to_host(gpu_preprocess(rowptr, colidx, n, 16))
     assert_tcb_equal(got, want, "big window")
+
+
+@pytest.mark.parametrize("bw", [16, 8])
+@pytest.mark.parametrize("kind", ["shuffled", "repeated", "both"])
+def test_preprocess_unsorted_rows_and_repeated_edges(kind, bw):
+    """CSR rows whose columns are not ascending, or that hold the same edge twice, are legal input for the
+    reference (src/utils.cu:173-224 walks the edges in CSR order): the tile ids of a TC block then follow CSR
+    order, not position order.  Windows of every size class: warp-per-window (a few edges), CTA one-pass
+    (hundreds to thousands of edges) and the general path (more than 16 384 edges)."""
+    n = 5000
+    rng = np.random.default_rng(11 if kind == "shuffled" else 12)
+    deg = rng.integers(0, 6, size=n).astype(np.int64)
+    deg[160:400] = rng.integers(40, 300, size=240)  # fifteen windows of 600..4800 edges
+    deg[800:816] = 1500                             # one window of 24 000 edges
+    cols = []
+    for d in deg:
+        c = rng.choice(n, size=int(d), replace=kind != "shuffled") if d else np.zeros(0, np.int64)
+        if kind == "repeated":
+            c = np.sort(c)
+        cols.append(c)
+    # one window stays clean (ascending, distinct) between dirty ones
+    for r in range(320, 336):
+        cols[r] = np.sort(rng.choice(n, size=int(deg[r]), replace=False))
+    rowptr = np.zeros(n + 1, np.int32)
+    rowptr[1:] = np.cumsum(deg)
+    colidx = np.concatenate(cols).astype(np.int32)
+    want = po.preprocess(colidx, rowptr, n, 16, bw)
+    got = to_host(gpu_preprocess(rowptr, colidx, n, bw))
+    assert_tcb_equal(got, want, f"{kind} bw={bw}")
 
 
 def test_preprocess_empty_and_degenerate():
