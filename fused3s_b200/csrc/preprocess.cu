@@ -32,7 +32,7 @@ constexpr int WIN_CAP = 4096;  // largest window (edges) sorted entirely in shar
 constexpr int SCHED_THREADS = 1024;
 constexpr int SCHED_WARPS = SCHED_THREADS / 32;
 
-enum { PH_ERROR = 0, PH_MAX_TCB = 1, PH_SUM_TCB = 2, PH_N_LARGE = 3, PH_N_LARGE_FILL = 4, PH_FILL_NEXT = 5, PH_INTS = 16 };
+enum { PH_ERROR = 0, PH_MAX_TCB = 1, PH_SUM_TCB = 2, PH_N_LARGE = 3, PH_N_LARGE_FILL = 4, PH_FILL_NEXT = 5, PH_RANK_NEXT = 6, PH_INTS = 16 };
 
 // ---- block-wide helpers ---------------------------------------------------------------
 
@@ -209,6 +209,30 @@ __device__ __forceinline__ int lower_bound_dev(const int *a, int n, int key) {
 constexpr int SMALL_N = 512;
 constexpr int SW_WARPS = 8;
 
+// Requests the 128-byte lines of a[0 .. n) into L2 (no data returned, nothing waits for it).
+__device__ __forceinline__ void prefetch_l2_lines(const int *a, int n, int tid, int n_threads) {
+  for (int i = tid * 32; i < n; i += n_threads * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(a + i));
+  if (tid == 0 && n > 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(a + n - 1));
+}
+
+// What a CTA of window_rank_kernel needs to know about entry li of its window list (nothing is loaded past the list).
+struct RankWindow {
+  int w, s, n;
+};
+__device__ __forceinline__ RankWindow rank_window(int li, int n_large, const int *__restrict__ large_list,
+                                                  const int *__restrict__ rowptr, int n_nodes) {
+  RankWindow f = {0, 0, 0};
+  if (li < n_large) {
+    f.w = large_list[li];
+    const int row0 = f.w * 16, row1 = min(row0 + 16, n_nodes);
+    f.s = rowptr[row0];
+    f.n = rowptr[row1] - f.s;
+  }
+  return f;
+}
+constexpr int RANK_AHEAD = 4;  // loads a thread keeps in flight in the passes over a window's edges
+constexpr int RANK_KREG = 32;  // edges per thread that stay in registers between the passes
+
 // ---- phase 1 --------------------------------------------------------------------------
 // One CTA per 16-row window.  Restates, for the whole window at once, what the reference's
 // sort (src/utils.cu:281-289) + generate_edgetocolumn (src/utils.cu:131-153) + fill_edgeToRow
@@ -223,36 +247,68 @@ constexpr int RANK_SMEM_BYTES = 2 * BM_WORDS * (int)sizeof(int);
 constexpr int RANK_DBITS = 10;
 static_assert(2 * WIN_CAP + (WIN_WARPS << RANK_DBITS) <= 2 * BM_WORDS, "the sort path's buffers share the bitmap path's memory");
 
-__global__ void __launch_bounds__(WIN_THREADS)
+__global__ void __launch_bounds__(WIN_THREADS, 3)  // three CTAs per SM: 64 KB of shared memory, 85 registers each
 window_rank_kernel(const int *__restrict__ colidx, const int *__restrict__ rowptr, int n_nodes, int n_cols,
                    int bw, const int *__restrict__ large_list, int *__restrict__ block_partition,
                    int *__restrict__ e2c, int *__restrict__ e2r, int *scratch_a, int *scratch_b, int *hdr) {
   extern __shared__ __align__(16) int dsm[];
   __shared__ int s_aux[33];
   __shared__ int s_min[WIN_WARPS], s_max[WIN_WARPS];
+  __shared__ int s_rp[17];  // row pointers of the window
+  __shared__ int s_next;
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   const int n_large = hdr[PH_N_LARGE];  // windows with more than SMALL_N edges, listed by window_rank_small
-  for (int li = blockIdx.x; li < n_large; li += gridDim.x) {
-  __syncthreads();  // the previous window's shared memory is no longer read
-  const int w = large_list[li];
-  const int row0 = w * 16, row1 = min(row0 + 16, n_nodes);
-  const int s = rowptr[row0], t = rowptr[row1];
-  const int n = t - s;
+  // A CTA pulls its windows from a counter and always knows the next one: its header is loaded, and its slice
+  // of colIdx is requested into L2, while the current window is worked on (a pass over a window's edges
+  // otherwise pays DRAM latency per step).
+  if (tid == 0) s_next = atomicAdd(&hdr[PH_RANK_NEXT], 1);
+  __syncthreads();
+  int li = s_next;
+  RankWindow ahead = rank_window(li, n_large, large_list, rowptr, n_nodes);
+  for (;;) {
+  __syncthreads();  // the previous window's shared memory (and s_next) is no longer read
+  if (li >= n_large) break;
+  if (tid == 0) s_next = atomicAdd(&hdr[PH_RANK_NEXT], 1);
+  const int w = ahead.w, s = ahead.s, n = ahead.n, t = s + n;
+  const int row0 = w * 16;
+  if (tid < 17) s_rp[tid] = rowptr[min(row0 + tid, n_nodes)];
+  __syncthreads();
+  li = s_next;
+  ahead = rank_window(li, n_large, large_list, rowptr, n_nodes);  // used after the first pass below
 
-  // row of every edge; column range of the window; columns outside [0, n_cols) are an error
-  for (int r = row0 + warp; r < row1; r += WIN_WARPS) {
-    const int a = rowptr[r], b = rowptr[r + 1];
-    for (int e = a + lane; e < b; e += 32) e2r[e] = r;
-  }
+  // column range of the window; columns outside [0, n_cols) are an error
   int cmin = INT_MAX, cmax = INT_MIN;
   bool bad = false;
-  for (int e = s + tid; e < t; e += WIN_THREADS) {
-    const int c = colidx[e];
-    bad |= (c < 0) | (c >= n_cols);
-    cmin = min(cmin, c);
-    cmax = max(cmax, c);
+  // The first RANK_KREG * WIN_THREADS edges of the window stay in registers for all three passes (all their
+  // loads are in flight together); what lies beyond is re-read, RANK_AHEAD loads at a time.  Slots past the
+  // window's end repeat its last edge: harmless for the range and the occupancy bits, skipped when writing.
+  int cv[RANK_KREG];
+#pragma unroll
+  for (int u = 0; u < RANK_KREG; ++u) {
+    if (u * WIN_THREADS >= n) break;  // uniform; the later passes stop at the same slot
+    cv[u] = colidx[min(s + tid + u * WIN_THREADS, t - 1)];
   }
+#pragma unroll
+  for (int u = 0; u < RANK_KREG; ++u) {
+    if (u * WIN_THREADS >= n) break;
+    bad |= (cv[u] < 0) | (cv[u] >= n_cols);
+    cmin = min(cmin, cv[u]);
+    cmax = max(cmax, cv[u]);
+  }
+  const int s_mem = s + RANK_KREG * WIN_THREADS;  // first edge that is not held in registers
+  for (int e0 = s_mem + tid; e0 < t; e0 += WIN_THREADS * RANK_AHEAD) {
+    int c[RANK_AHEAD];
+#pragma unroll
+    for (int u = 0; u < RANK_AHEAD; ++u) c[u] = colidx[min(e0 + u * WIN_THREADS, t - 1)];  // in flight together
+#pragma unroll
+    for (int u = 0; u < RANK_AHEAD; ++u) {
+      bad |= (c[u] < 0) | (c[u] >= n_cols);
+      cmin = min(cmin, c[u]);
+      cmax = max(cmax, c[u]);
+    }
+  }
+  prefetch_l2_lines(colidx + ahead.s, ahead.n, tid, WIN_THREADS);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     cmin = min(cmin, __shfl_xor_sync(0xffffffffu, cmin, o));
@@ -265,6 +321,11 @@ window_rank_kernel(const int *__restrict__ colidx, const int *__restrict__ rowpt
   if (__syncthreads_or(bad)) {  // the host reports the error; nothing else of this window is needed
     if (tid == 0) atomicExch(&hdr[PH_ERROR], 1);
     continue;
+  }
+  // row of every edge (the row pointers came in above)
+  for (int r = warp; r < 16; r += WIN_WARPS) {
+    const int a = s_rp[r], b = s_rp[r + 1];
+    for (int e = a + lane; e < b; e += 32) e2r[e] = row0 + r;
   }
 #pragma unroll
   for (int i = 0; i < WIN_WARPS; ++i) {
@@ -281,9 +342,18 @@ window_rank_kernel(const int *__restrict__ colidx, const int *__restrict__ rowpt
     const int nw = (int)words;
     for (int i = tid; i < nw; i += WIN_THREADS) bm[i] = 0u;
     __syncthreads();
-    for (int e = s + tid; e < t; e += WIN_THREADS) {
-      const int c = colidx[e] - cmin;
-      atomicOr(&bm[c >> 5], 1u << (c & 31));
+#pragma unroll
+    for (int u = 0; u < RANK_KREG; ++u) {
+      if (u * WIN_THREADS >= n) break;  // uniform
+      const int c = cv[u] - cmin;
+      atomicOr(&bm[c >> 5], 1u << (c & 31));  // repeats set the same bit
+    }
+    for (int e0 = s_mem + tid; e0 < t; e0 += WIN_THREADS * RANK_AHEAD) {
+      int c[RANK_AHEAD];
+#pragma unroll
+      for (int u = 0; u < RANK_AHEAD; ++u) c[u] = colidx[min(e0 + u * WIN_THREADS, t - 1)] - cmin;
+#pragma unroll
+      for (int u = 0; u < RANK_AHEAD; ++u) atomicOr(&bm[c[u] >> 5], 1u << (c[u] & 31));
     }
     __syncthreads();
     const int per = ((nw + WIN_THREADS - 1) / WIN_THREADS) | 1;  // odd: consecutive threads hit different banks
@@ -296,10 +366,24 @@ window_rank_kernel(const int *__restrict__ colidx, const int *__restrict__ rowpt
       run += __popc(bm[i]);
     }
     __syncthreads();
-    for (int e = s + tid; e < t; e += WIN_THREADS) {
-      const int c = colidx[e] - cmin;
+#pragma unroll
+    for (int u = 0; u < RANK_KREG; ++u) {
+      if (u * WIN_THREADS >= n) break;
+      const int e = s + tid + u * WIN_THREADS;
+      const int c = cv[u] - cmin;
       const int wi = c >> 5;
-      e2c[e] = pre[wi] + __popc(bm[wi] & ((1u << (c & 31)) - 1u));
+      if (e < t) e2c[e] = pre[wi] + __popc(bm[wi] & ((1u << (c & 31)) - 1u));
+    }
+    for (int e0 = s_mem + tid; e0 < t; e0 += WIN_THREADS * RANK_AHEAD) {
+      int c[RANK_AHEAD];
+#pragma unroll
+      for (int u = 0; u < RANK_AHEAD; ++u) c[u] = colidx[min(e0 + u * WIN_THREADS, t - 1)] - cmin;
+#pragma unroll
+      for (int u = 0; u < RANK_AHEAD; ++u) {
+        const int e = e0 + u * WIN_THREADS;
+        const int wi = c[u] >> 5;
+        if (e < t) e2c[e] = pre[wi] + __popc(bm[wi] & ((1u << (c[u] & 31)) - 1u));
+      }
     }
   } else {
     // ---- stable radix sort of the window's columns, distinct compaction, binary search
@@ -514,12 +598,6 @@ __device__ __forceinline__ FillWindow fill_window(int li, int n_large, const int
     f.nb = rwo[f.w + 1] - f.tcb0;
   }
   return f;
-}
-
-// Requests the 128-byte lines of a[0 .. n) into L2 (no data returned, nothing waits for it).
-__device__ __forceinline__ void prefetch_l2_lines(const int *a, int n, int tid, int n_threads) {
-  for (int i = tid * 32; i < n; i += n_threads * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(a + i));
-  if (tid == 0 && n > 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(a + n - 1));
 }
 
 // Tile ids (row * BW + column) of the occupied positions of one TC block in row-major order, from its
