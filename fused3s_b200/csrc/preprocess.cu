@@ -254,28 +254,45 @@ window_rank_kernel(const int *__restrict__ colidx, const int *__restrict__ rowpt
   extern __shared__ __align__(16) int dsm[];
   __shared__ int s_aux[33];
   __shared__ int s_min[WIN_WARPS], s_max[WIN_WARPS];
-  __shared__ int s_rp[17];  // row pointers of the window
-  __shared__ int s_next;
+  __shared__ int s_rp2[2][17];  // row pointers of the current and of the next window
+  __shared__ int s_pull;
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
   const int n_large = hdr[PH_N_LARGE];  // windows with more than SMALL_N edges, listed by window_rank_small
-  // A CTA pulls its windows from a counter and always knows the next one: its header is loaded, and its slice
-  // of colIdx is requested into L2, while the current window is worked on (a pass over a window's edges
-  // otherwise pays DRAM latency per step).
-  if (tid == 0) s_next = atomicAdd(&hdr[PH_RANK_NEXT], 1);
+  // A CTA pulls its windows from a counter, two ahead: while window k is worked on, the header and the row
+  // pointers of window k+1 are loaded and its slice of colIdx is requested into L2 (a pass over a window's
+  // edges otherwise pays DRAM latency per step), and the counter is read for window k+2 -- none of these
+  // round trips is waited for.
+  if (tid == 0) s_pull = atomicAdd(&hdr[PH_RANK_NEXT], 2);
   __syncthreads();
-  int li = s_next;
-  RankWindow ahead = rank_window(li, n_large, large_list, rowptr, n_nodes);
-  for (;;) {
-  __syncthreads();  // the previous window's shared memory (and s_next) is no longer read
+  int li = s_pull, li_next = li + 1, pulled = 0, buf = 0;
+  RankWindow cur = rank_window(li, n_large, large_list, rowptr, n_nodes), ahead = cur;
+  if (tid < 17 && li < n_large) s_rp2[0][tid] = rowptr[min(cur.w * 16 + tid, n_nodes)];
+  bool staged = true;
+  auto stage_next = [&]() {  // what the next window needs from memory, asked for while this one is worked on
+    if (staged) return;
+    staged = true;
+    prefetch_l2_lines(colidx + ahead.s, ahead.n, tid, WIN_THREADS);
+    if (tid < 17 && li_next < n_large) s_rp2[buf ^ 1][tid] = rowptr[min(ahead.w * 16 + tid, n_nodes)];
+  };
+  auto advance = [&]() {
+    stage_next();
+    if (tid == 0) s_pull = pulled;
+    __syncthreads();
+    li = li_next;
+    li_next = s_pull;
+    cur = ahead;
+    buf ^= 1;
+  };
+  for (;; advance()) {
+  __syncthreads();  // the previous window's shared memory (and s_pull) is no longer read
   if (li >= n_large) break;
-  if (tid == 0) s_next = atomicAdd(&hdr[PH_RANK_NEXT], 1);
-  const int w = ahead.w, s = ahead.s, n = ahead.n, t = s + n;
+  if (tid == 0) pulled = atomicAdd(&hdr[PH_RANK_NEXT], 1);  // consumed in advance()
+  ahead = rank_window(li_next, n_large, large_list, rowptr, n_nodes);  // consumed in stage_next()
+  staged = false;
+  const int *s_rp = s_rp2[buf];
+  const int w = cur.w, s = cur.s, n = cur.n, t = s + n;
   const int row0 = w * 16;
-  if (tid < 17) s_rp[tid] = rowptr[min(row0 + tid, n_nodes)];
-  __syncthreads();
-  li = s_next;
-  ahead = rank_window(li, n_large, large_list, rowptr, n_nodes);  // used after the first pass below
 
   // column range of the window; columns outside [0, n_cols) are an error
   int cmin = INT_MAX, cmax = INT_MIN;
@@ -308,7 +325,7 @@ window_rank_kernel(const int *__restrict__ colidx, const int *__restrict__ rowpt
       cmax = max(cmax, c[u]);
     }
   }
-  prefetch_l2_lines(colidx + ahead.s, ahead.n, tid, WIN_THREADS);
+  stage_next();
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     cmin = min(cmin, __shfl_xor_sync(0xffffffffu, cmin, o));
@@ -563,7 +580,7 @@ constexpr int FILL_THREADS = 512;
 constexpr int FILL_WARPS = FILL_THREADS / 32;
 constexpr int FILL_DBITS = 10;  // NB_CAP TC blocks in one pass
 constexpr int FILL_KREG = 32;   // edges per thread on the one-pass path
-constexpr int FILL_AHEAD = 4;   // steps of the edge walk whose loads are in flight together
+constexpr int FILL_AHEAD = 8;   // steps of the edge walk whose loads are in flight together
 constexpr int FILL_HIST_INTS = FILL_WARPS << FILL_DBITS;
 constexpr int FILL_SMEM_BYTES = (FILL_HIST_INTS + NB_CAP) * (int)sizeof(int) + NB_CAP * 4 * 8;
 static_assert((1 << FILL_DBITS) >= NB_CAP, "one radix pass must cover every TCB id of the one-pass path");
@@ -646,8 +663,9 @@ window_fill_kernel(const int *__restrict__ colidx, const int *__restrict__ rowpt
                    unsigned long long *__restrict__ bitmap, int *scratch_a, int *scratch_b) {
   extern __shared__ __align__(16) int dsm[];
   __shared__ int s_aux[33];
-  __shared__ int s_rp[17];  // row pointers of the window: the row of an edge follows from its position
-  __shared__ int s_next;
+  __shared__ int s_rp2[2][17];  // row pointers of the current and of the next window: the row of an edge follows
+                                // from its position
+  __shared__ int s_pull;
   int *s_hist = dsm, *s_cnt = s_hist + FILL_HIST_INTS;
   unsigned long long *s_bmp = reinterpret_cast<unsigned long long *>(s_cnt + NB_CAP);
   unsigned *s_bmp32 = reinterpret_cast<unsigned *>(s_bmp);
@@ -657,22 +675,41 @@ window_fill_kernel(const int *__restrict__ colidx, const int *__restrict__ rowpt
   const int sub_per_col = bw / 8;
   const int lbw = (bw == 16) ? 4 : 3;
   const bool vec16 = ((reinterpret_cast<uintptr_t>(bitmap) | reinterpret_cast<uintptr_t>(atox)) & 15) == 0;
-  // A CTA pulls its windows from a counter (they differ in size by 10x) and always knows the next one: that
-  // window's header is loaded, and its slices of edgeToColumn and colIdx are requested into L2, while the
-  // current window is worked on -- the walk over a window's edges otherwise pays DRAM latency per step.
-  if (tid == 0) s_next = atomicAdd(&hdr[PH_FILL_NEXT], 1);
+  // A CTA pulls its windows from a counter (they differ in size by 10x), two ahead: while window k is worked
+  // on, the header and the row pointers of window k+1 are loaded and its slices of edgeToColumn and colIdx are
+  // requested into L2 (the walk over a window's edges otherwise pays DRAM latency per step), and the counter is
+  // read for window k+2 -- none of these round trips is waited for.
+  if (tid == 0) s_pull = atomicAdd(&hdr[PH_FILL_NEXT], 2);
   __syncthreads();
-  int li = s_next;
-  FillWindow ahead = fill_window(li, n_large, large_list, rowptr, rwo, n_nodes);
-  for (;;) {
-    __syncthreads();  // the previous window's shared memory (and s_next) is no longer read
-    if (li >= n_large) break;
-    if (tid == 0) s_next = atomicAdd(&hdr[PH_FILL_NEXT], 1);
+  int li = s_pull, li_next = li + 1, pulled = 0, buf = 0;
+  FillWindow cur = fill_window(li, n_large, large_list, rowptr, rwo, n_nodes), ahead = cur;
+  if (tid < 17 && li < n_large) s_rp2[0][tid] = rowptr[min(cur.w * 16 + tid, n_nodes)];
+  bool staged = true;
+  auto stage_next = [&]() {  // what the next window needs from memory, asked for while this one is worked on
+    if (staged) return;
+    staged = true;
+    prefetch_l2_lines(e2c + ahead.s, ahead.n, tid, FILL_THREADS);
+    prefetch_l2_lines(colidx + ahead.s, ahead.n, tid, FILL_THREADS);
+    if (tid < 17 && li_next < n_large) s_rp2[buf ^ 1][tid] = rowptr[min(ahead.w * 16 + tid, n_nodes)];
+  };
+  auto advance = [&]() {
+    stage_next();
+    if (tid == 0) s_pull = pulled;
     __syncthreads();
-    const int w = ahead.w, s = ahead.s, n = ahead.n, tcb0 = ahead.tcb0, nb = ahead.nb;
-    const int row0 = w * 16, tcb1 = tcb0 + nb;
-    li = s_next;
-    ahead = fill_window(li, n_large, large_list, rowptr, rwo, n_nodes);  // used after the walk below
+    li = li_next;
+    li_next = s_pull;
+    cur = ahead;
+    buf ^= 1;
+  };
+  for (;; advance()) {
+    __syncthreads();  // the previous window's shared memory (and s_pull) is no longer read
+    if (li >= n_large) break;
+    if (tid == 0) pulled = atomicAdd(&hdr[PH_FILL_NEXT], 1);  // consumed in advance()
+    ahead = fill_window(li_next, n_large, large_list, rowptr, rwo, n_nodes);  // consumed in stage_next()
+    staged = false;
+    const int *s_rp = s_rp2[buf];
+    const int w = cur.w, s = cur.s, n = cur.n, tcb0 = cur.tcb0, nb = cur.nb;
+    const int tcb1 = tcb0 + nb;
     if (nb <= 0) continue;
     const bool in_smem = nb <= NB_CAP;
     int bits = 0;
@@ -685,7 +722,6 @@ window_fill_kernel(const int *__restrict__ colidx, const int *__restrict__ rowpt
       // memory.  If every row's columns ascend strictly (checked in the first walk), the CSR order of the edges
       // inside a TC block is the row-major order of its occupancy bits, so the tile ids and the per-block edge
       // counts follow from the occupancy words alone: one thread per TC block, no second walk, no sort.
-      if (tid < 17) s_rp[tid] = rowptr[min(row0 + tid, n_nodes)];
       int *s_atox = s_hist;  // at most NB_CAP * 16 = FILL_HIST_INTS column slots
       bool slow = false;
       int edges_done = 0;
@@ -744,8 +780,7 @@ window_fill_kernel(const int *__restrict__ colidx, const int *__restrict__ rowpt
         }
         if (tl0 == 0) {
           slow = __syncthreads_or(unsorted);
-          prefetch_l2_lines(e2c + ahead.s, ahead.n, tid, FILL_THREADS);
-          prefetch_l2_lines(colidx + ahead.s, ahead.n, tid, FILL_THREADS);
+          stage_next();
           if (slow && !(in_smem && n <= FILL_KREG * FILL_THREADS)) break;  // left to the general path
         } else {
           __syncthreads();
