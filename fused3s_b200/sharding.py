@@ -30,6 +30,8 @@ another rank: the only inter-rank synchronisation is the NCCL collective itself.
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 
 import numpy as np
@@ -120,6 +122,57 @@ def make_shard(rowptr: np.ndarray, colidx: np.ndarray, num_nodes: int, rank: int
                     int(np.max(np.diff(cuts))), local_last)
 
 
+class CollectiveError(RuntimeError):
+    """A collective of the sharded path did not complete (a peer never joined, or the backend reported an
+    error).  The reference has no counterpart (it is single-GPU); this is the host-side failure report of
+    the multi-GPU layer: nothing on a GPU waits without a limit, the host learns of the failure."""
+
+
+_collective_timeout_s: float | None = (
+    float(os.environ["F3S_COLLECTIVE_TIMEOUT_S"]) if os.environ.get("F3S_COLLECTIVE_TIMEOUT_S") else None
+)
+
+
+def set_collective_timeout(seconds: float | None) -> float | None:
+    """Guarded mode for every NCCL / gloo collective of this module: ``seconds`` = host-side limit per
+    collective (``None`` = off, the default: collectives are enqueued and never polled).  Returns the previous
+    value.  In guarded mode a collective is issued asynchronously, the host polls its completion and raises
+    ``CollectiveError`` naming the collective and the rank when the limit passes or the backend reports an
+    error -- at the price of one host synchronisation per collective, so it is a diagnosis mode, not the
+    timed path.  (The multicast all-gather of torch symmetric memory returns no work handle and is not
+    covered; its set-up is checked once, see ``ShardedAttention``.)"""
+    global _collective_timeout_s
+    prev = _collective_timeout_s
+    _collective_timeout_s = None if seconds is None else float(seconds)
+    return prev
+
+
+def _run_collective(name, issue, group=None):
+    """``issue(async_op)`` enqueues one collective and returns its work handle (or None)."""
+    import time
+
+    import torch.distributed as dist
+
+    limit = _collective_timeout_s
+    if limit is None:
+        issue(False)
+        return
+    where = f"{name} on rank {dist.get_rank(group)} of {dist.get_world_size(group)}"
+    try:
+        work = issue(True)
+        deadline = time.monotonic() + limit
+        while work is not None and not work.is_completed():
+            if time.monotonic() > deadline:
+                raise CollectiveError(f"{where}: not complete after {limit:g} s (a peer that never joined?)")
+            time.sleep(0.0005)
+        if work is not None:
+            work.wait()  # orders the current stream after the collective; raises what the backend recorded
+    except CollectiveError:
+        raise
+    except Exception as exc:  # noqa: BLE001 -- whatever the backend raises is reported with its context
+        raise CollectiveError(f"{where}: {exc}") from exc
+
+
 def all_gather_padded(local_padded, full_padded, group=None):
     """``full_padded`` ([world*max_rows, ...]) <- every rank's ``local_padded`` ([max_rows, ...])."""
     import torch.distributed as dist
@@ -129,10 +182,13 @@ def all_gather_padded(local_padded, full_padded, group=None):
         full_padded.copy_(local_padded)
         return full_padded
     if dist.get_backend(group) == "nccl":
-        dist.all_gather_into_tensor(full_padded, local_padded, group=group)
+        _run_collective("all_gather_into_tensor",
+                        lambda a: dist.all_gather_into_tensor(full_padded, local_padded, group=group, async_op=a),
+                        group)
     else:  # gloo (CPU tests)
         chunks = list(full_padded.view((world,) + tuple(local_padded.shape)).unbind(0))
-        dist.all_gather(chunks, local_padded.contiguous(), group=group)
+        _run_collective("all_gather",
+                        lambda a: dist.all_gather(chunks, local_padded.contiguous(), group=group, async_op=a), group)
     return full_padded
 
 
@@ -153,7 +209,7 @@ def all_gather_rows(local, row_cuts, full=None, group=None):
     pad = torch.zeros((max_rows,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
     pad[: local.shape[0]] = local
     gathered = [torch.empty_like(pad) for _ in range(world)]
-    dist.all_gather(gathered, pad, group=group)
+    _run_collective("all_gather", lambda a: dist.all_gather(gathered, pad, group=group, async_op=a), group)
     for r in range(world):
         a, b = int(row_cuts[r]), int(row_cuts[r + 1])
         full[a:b].copy_(gathered[r][: b - a])
@@ -414,10 +470,7 @@ class HeadShardedAttention:
         rows, _, d = x_rows.shape
         send = x_rows.view(rows, w, hl, d).permute(1, 0, 2, 3).contiguous()  # [W(dest), rows, hl, d]
         recv = torch.empty_like(send)  # [W(src), rows, hl, d] == [N, hl, d]
-        if w == 1 or not dist.is_initialized():
-            recv.copy_(send)
-        else:
-            dist.all_to_all_single(recv, send)
+        _all_to_all(recv, send)
         return recv.view(w * rows, hl, d)
 
     def _heads_to_rows(self, x_heads):
@@ -430,10 +483,7 @@ class HeadShardedAttention:
         rows = n // w
         send = x_heads.view(w, rows, hl, d)  # chunk j = rows of rank j, contiguous
         recv = torch.empty_like(send)  # [W(src = head group), rows, hl, d]
-        if w == 1 or not dist.is_initialized():
-            recv.copy_(send)
-        else:
-            dist.all_to_all_single(recv, send.contiguous())
+        _all_to_all(recv, send.contiguous())
         return recv.permute(1, 0, 2, 3).reshape(rows, w * hl, d)
 
     def forward_from_rows(self, q_rows, k_rows, v_rows, scale_divisor: float = 1.0):
@@ -452,7 +502,8 @@ def _all_to_all(recv, send, group=None):
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         recv.copy_(send)
     else:
-        dist.all_to_all_single(recv, send, group=group)
+        _run_collective("all_to_all_single",
+                        lambda a: dist.all_to_all_single(recv, send, group=group, async_op=a), group)
 
 
 class HeadShardedPipeline:

@@ -211,3 +211,39 @@ def test_phase_split_array_names_the_only_block_with_columns_of_both_kinds():
             # blocks before lb - 1 hold nothing at or above the split (padding slots of a last block are 0)
             for t in range(a, max(a, lb - 1)):
                 assert int(atox[t].max()) < split
+
+
+def _guard_worker(rank, world, port, out_file):
+    """Host-made failure: rank 1 joins the first collective and then never calls the second one."""
+    import time
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    assert sharding.set_collective_timeout(1.5) is None
+    local = torch.full((4, 3), float(rank + 1))
+    full = torch.zeros(world * 4, 3)
+    sharding.all_gather_padded(local, full)  # guarded, every rank joins: completes, result as without the guard
+    ok = bool(torch.equal(full[:4], torch.full((4, 3), 1.0)) and torch.equal(full[4:], torch.full((4, 3), 2.0)))
+    recv = torch.zeros(world, 2)
+    sharding._all_to_all(recv, torch.full((world, 2), float(rank)))
+    ok = ok and bool(torch.equal(recv[:, 0], torch.arange(world, dtype=torch.float32)))
+    if rank == 1:
+        time.sleep(4.0)  # never joins the next collective; leaves between steps, nothing of its own in flight
+        os._exit(0)
+    t0 = time.monotonic()
+    try:
+        sharding.all_gather_padded(local, full)
+        outcome = "completed"
+    except sharding.CollectiveError as e:
+        outcome = "raised" if ("rank 0 of 2" in str(e) and "all_gather" in str(e)) else f"wrong message: {e}"
+    torch.save({"ok": ok, "outcome": outcome, "seconds": time.monotonic() - t0}, out_file)
+    os._exit(0)  # the abandoned collective would block an orderly shutdown of the process group
+
+
+def test_guarded_collective_reports_a_rank_that_never_joins(tmp_path):
+    out_file = str(tmp_path / "res.pt")
+    mp.spawn(_guard_worker, args=(2, _free_port(), out_file), nprocs=2, join=True)
+    res = torch.load(out_file)
+    assert res["ok"] and res["outcome"] == "raised", res
+    assert 1.4 <= res["seconds"] <= 3.5, res
