@@ -11,10 +11,15 @@
 //       bits.  Otherwise a stable LSD radix sort (shared memory, or an L2-resident slice of
 //       the workspace), distinct compaction and binary search.
 //   scan -> window offsets, one device->host copy of the TCB count.
-//   phase 2 (window_fill_small / window_fill_kernel): original-column list, occupancy bitmaps
-//       and per-TCB edge counts (accumulated in shared memory, stored once), and the tile ids
-//       regrouped by TCB with a stable radix sort (key = TCB id inside the window, payload =
-//       tile id, packed in one word).
+//   phase 2 (window_fill_small / window_fill_kernel): original-column list and occupancy
+//       bitmaps (assembled in shared memory, stored once), per-TCB edge counts and the tile ids
+//       regrouped by TCB.  The CTA kernel derives counts and tile ids from the occupancy words
+//       alone when every row's columns ascend strictly (CSR order inside a TC block is then the
+//       row-major order of its bits); otherwise, and in the warp kernel, a stable radix sort
+//       (key = TCB id inside the window, payload = tile id, packed in one word) regroups them.
+//   The CTA kernels pull their windows from a counter and ask for the next window's header, row
+//   pointers and edge slices (prefetch into L2) while the current one is worked on: a pass over
+//   a window's edges is otherwise bound by one DRAM round trip per step.
 //   scan -> TCB edge offsets; one CTA radix-sorts the windows by TCB count (descending,
 //       stable) for the schedule.
 // Outputs are bit-identical to the reference's arrays for inputs on which its
@@ -569,12 +574,11 @@ window_rank_small(const int *__restrict__ colidx, const int *__restrict__ rowptr
 // order inside a TCB) with a stable radix sort on the TCB bits.
 //
 // CTA per window (windows with more than SMALL_N edges, taken from the list window_fill_small
-// builds).  Walking the edges costs one round of global-memory latency per pass, so the common case
-// makes ONE pass: a thread keeps the (TCB id, tile id) words of its edges in registers, the per-warp
-// histogram of the single radix pass is filled in the same loop, the stable scatter writes the tile
-// bytes into shared memory and they leave with coalesced stores.  Windows with more than
-// FILL_KREG * FILL_THREADS edges or more than NB_CAP TC blocks take the general path: the words go
-// through the workspace (L2) and a multi-pass radix sort.
+// builds).  Windows of up to FILL_STAGE_MAX edges take their TC blocks NB_CAP at a time and make one
+// walk over their edges per range (column list and occupancy words in shared memory); sorted rows
+// need nothing else, unsorted ones of up to FILL_KREG * FILL_THREADS edges and NB_CAP TC blocks keep
+// their (TCB id, tile id) words in registers for a single stable radix pass.  Everything else takes
+// the general path: the words go through the workspace (L2) and a multi-pass radix sort.
 constexpr int NB_CAP = 1024;
 constexpr int FILL_THREADS = 512;
 constexpr int FILL_WARPS = FILL_THREADS / 32;
