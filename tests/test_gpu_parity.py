@@ -119,6 +119,49 @@ def test_preprocess_unsorted_rows_and_repeated_edges(kind, bw):
     assert_tcb_equal(got, want, f"{kind} bw={bw}")
 
 
+@pytest.mark.parametrize("bw", [16, 8])
+def test_preprocess_fill_into_output_arrays_off_a_16_byte_boundary(bw):
+    """The C ABI takes plain pointers: output arrays that start on their natural alignment only (4 bytes for
+    sparseAToXidx, 8 for the occupancy words, 1 for the tile ids) take the fill kernel's scalar stores instead of
+    its 16-byte ones and must hold the same values."""
+    import ctypes as C
+
+    c = cabi()
+    n = 3000
+    rng = np.random.default_rng(21)
+    deg = rng.integers(0, 8, size=n).astype(np.int64)
+    deg[64:160] = rng.integers(60, 400, size=96)  # six windows for the CTA kernel
+    cols = [np.sort(rng.choice(n, size=int(d), replace=False)) for d in deg]
+    rowptr = np.zeros(n + 1, np.int32)
+    rowptr[1:] = np.cumsum(deg)
+    colidx = np.concatenate(cols).astype(np.int32)
+    rp, ci = torch.from_numpy(rowptr).to(DEV), torch.from_numpy(colidx).to(DEV)
+    ref = c.preprocess(ci, rp, n, bw)
+    nt, nnz, wpt, n_rw = ref["nTCB"], len(colidx), 16 * bw // 64, (n + 15) // 16
+    i32 = dict(dtype=torch.int32, device=DEV)
+    atox = torch.zeros(nt * bw + 4, **i32)[1:1 + nt * bw]
+    bitmap = torch.zeros(nt * wpt + 2, dtype=torch.int64, device=DEV)[1:1 + nt * wpt]
+    tile = torch.zeros(nnz + 16, dtype=torch.uint8, device=DEV)[3:3 + nnz]
+    assert atox.data_ptr() % 16 == 4 and bitmap.data_ptr() % 16 == 8 and tile.data_ptr() % 16 == 3
+    rowid, off, srt = torch.empty(nt, **i32), torch.empty(nt + 1, **i32), torch.empty(n_rw, **i32)
+    l = c.lib()
+    ws_bytes = l.f3s_preprocess_workspace_bytes(n, nnz, bw)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=DEV)
+    ptr = lambda t: C.c_void_p(t.data_ptr())
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    c.check(l.f3s_preprocess_fill(ptr(ci), ptr(rp), n, nnz, 16, bw, ptr(ref["edgeToColumn"]), ptr(ref["edgeToRow"]),
+                                  ptr(ref["rowWindowOffset"]), nt, ptr(srt), ptr(rowid), ptr(tile), ptr(off),
+                                  ptr(atox), ptr(bitmap), ptr(ws), ws_bytes, stream))
+    torch.cuda.synchronize()
+    assert torch.equal(atox, ref["sparseAToXidx"]) and torch.equal(tile, ref["tcblocktile_id"])
+    assert torch.equal(bitmap, ref["tcbBitMap"].view(torch.int64))
+    assert torch.equal(off, ref["tcblock_offset"]) and torch.equal(rowid, ref["tcblock_rowid"])
+    assert torch.equal(srt, ref["sortedRowWindows"])
+    want = po.preprocess(colidx, rowptr, n, 16, bw)
+    assert np.array_equal(atox.cpu().numpy(), want["sparseAToXidx"])
+    assert np.array_equal(tile.cpu().numpy(), want["tcblocktile_id"])
+
+
 def test_preprocess_empty_and_degenerate():
     c = cabi()
     n = 40
