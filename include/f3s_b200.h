@@ -89,7 +89,10 @@ int f3s_preprocess_count_rect(const int32_t *colidx, const int32_t *rowptr, int3
  * (src/F3S.cpp:83-86): sorted_row_windows[nRW], tcblock_rowid[nTCB], tcblocktile_id[nnz],
  * tcblock_offset[nTCB+1], sparse_a_to_x_idx[nTCB*block_w], tcb_bitmap[nTCB*16*block_w/64].
  * All six arrays are fully written (padding slots and empty bitmaps become 0), so the
- * caller need not zero them.  Inputs are the arrays phase 1 produced.
+ * caller need not zero them.  Inputs are the arrays phase 1 produced.  The arrays need only their
+ * natural alignment; sparse_a_to_x_idx and tcb_bitmap that start on a 16-byte boundary (any torch
+ * or cudaMalloc allocation) are written with 16-byte stores.  Rows whose columns do not ascend, or
+ * that hold an edge twice, are legal (tile ids then follow CSR order, as in the reference).
  * Stands in for generate_tcblock_rowid_cuda, generate_tcoffset_id_atob_cuda, the second
  * scan and sort_row_windows_by_tcb_count (src/utils.cu:53-78, 173-267, 310-341, 400-436).
  */
