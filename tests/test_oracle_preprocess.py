@@ -151,3 +151,56 @@ def test_against_reference_arrays(path):
 
 def test_golden_reference_arrays_present():
     assert GOLDEN_TCB, "tests/golden/tcb_ref_*.npz missing: the preprocessing oracle would be unpinned"
+
+
+def _byte_perm(a, b, sel):
+    """PTX prmt.b32 (default mode): result byte i = byte (sel >> 4i) & 7 of the pair {b, a} (a = bytes 0..3)."""
+    by = [(a >> (8 * i)) & 255 for i in range(4)] + [(b >> (8 * i)) & 255 for i in range(4)]
+    return sum(by[(sel >> (4 * i)) & 7] << (8 * i) for i in range(4))
+
+
+def _tile_ids_from_words(words, bw):
+    """Host model of the fill kernel's sort-free path (fused3s_b200/csrc/preprocess.cu, tile_bytes_of_block):
+    the occupancy words of one TC block regrouped into 32-bit row-major words, tile id = 32 * word + clz."""
+    if bw == 16:
+        m = []
+        for h in range(2):
+            lh, ll = words[h] >> 32, words[h] & 0xFFFFFFFF
+            rh, rl = words[2 + h] >> 32, words[2 + h] & 0xFFFFFFFF
+            m += [_byte_perm(lh, rh, 0x3726), _byte_perm(lh, rh, 0x1504),
+                  _byte_perm(ll, rl, 0x3726), _byte_perm(ll, rl, 0x1504)]
+    else:
+        m = [x for h in range(2) for x in (words[h] >> 32, words[h] & 0xFFFFFFFF)]
+    out = []
+    for k, x in enumerate(m):
+        while x:
+            z = 32 - x.bit_length()
+            out.append(32 * k + z)
+            x &= ~(0x80000000 >> z)
+    return out
+
+
+@pytest.mark.parametrize("bw", [16, 8])
+def test_tile_ids_follow_from_occupancy_words_when_rows_ascend(bw):
+    """What the CUDA fill kernel relies on for sorted CSR rows: inside a TC block the CSR order of the edges is
+    the row-major order of its occupancy bits, so tcblocktile_id and tcblock_offset are functions of tcbBitMap
+    (src/utils.cu:173-224 writes them edge by edge).  Checked on the oracle's arrays, which are pinned to the
+    reference's."""
+    rowptr, colidx = random_csr(700, 60, 17, sort_cols=True, duplicates=False)
+    t = po.preprocess(colidx, rowptr, 700, 16, bw)
+    wpt = 16 * bw // 64
+    bm = t["tcbBitMap"].astype(np.uint64).reshape(-1, wpt)
+    off = t["tcblock_offset"]
+    assert t["nTCB"] > 100
+    for b in range(t["nTCB"]):
+        ids = _tile_ids_from_words([int(w) for w in bm[b]], bw)
+        assert len(ids) == off[b + 1] - off[b]
+        assert ids == [int(x) for x in t["tcblocktile_id"][off[b]:off[b + 1]]], b
+    # with an unsorted row the property fails, which is why the kernel checks the order first
+    rowptr2, colidx2 = random_csr(64, 40, 18, sort_cols=False, duplicates=False)
+    t2 = po.preprocess(colidx2, rowptr2, 64, 16, bw)
+    bm2 = t2["tcbBitMap"].astype(np.uint64).reshape(-1, wpt)
+    off2 = t2["tcblock_offset"]
+    same = all(_tile_ids_from_words([int(w) for w in bm2[b]], bw)
+               == [int(x) for x in t2["tcblocktile_id"][off2[b]:off2[b + 1]]] for b in range(t2["nTCB"]))
+    assert not same
